@@ -306,21 +306,31 @@ int llark_seq_qk_headnorm(const float* src, long long ld, int q_off, int k_off, 
                           void* kn, void* vraw, void* kring, void* vring, const int* tok_seq, const int* cu,
                           const int* pos0, const int* slot, int n_tok, int H, int G, int D, int cap, float eps,
                           int act_fp32, cudaStream_t stream);
+/* The same with values of their own: E columns per key / value head at v_off of src, copied (not normed) to vv
+ * [n_tok, G, E] and the value ring. temp_every > 0: the query at position p of its sequence is also multiplied by
+ * 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1). */
+int llark_seq_qkv_headnorm(const float* src, long long ld, int q_off, int k_off, int v_off, const float* wq,
+                           const float* wk, void* qn, void* kn, void* vv, void* kring, void* vring, const int* tok_seq,
+                           const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int cap,
+                           float eps, float temp_coef, int temp_every, int act_fp32, cudaStream_t stream);
 /* Sliding-window softmax attention: query at position i sees keys j with 0 <= i - j < window. Keys / values of this
  * step come from kn / vv ([n_tok, G, D] / [n_tok, G, E]), earlier ones from the rings [slots, cap, G, D|E] (entry
  * j % cap); from_ring_only = 1: the step's own token is already in the ring. score = q.k * scale_h[h]; the output is
- * multiplied by sigmoid(gate[t, h*E + e]) when gate != NULL. out [n_tok, H, E]. */
+ * multiplied by sigmoid(gate[t, h*E + e]) when gate != NULL (gate_per_head: by sigmoid(gate[t, h])). sink (optional)
+ * fp32 [H]: exp(sink[h]), unscaled, is one more term of head h's softmax denominator; it has no value. A window of at
+ * least cap positions with cap >= the longest sequence is plain causal attention. out [n_tok, H, E]. */
 int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                        const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
                        const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
-                       int cap, int from_ring_only, int act_fp32, cudaStream_t stream);
+                       int cap, int from_ring_only, const float* sink, int gate_per_head, int act_fp32,
+                       cudaStream_t stream);
 /* The same attention for steps that bring many tokens per request (prompts, portions): bf16 only, D = E a multiple of
  * 16 up to 256, 64-query CTAs on mma.sync with fp32 scores / softmax (csrc/seq_swa_mma.cu). max_len = the longest
  * request of the step. */
 int llark_seq_swa_attn_mma(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                            const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu,
                            const int* pos0, const int* slot, int n_seq, int max_len, int H, int G, int D, int window,
-                           int cap, cudaStream_t stream);
+                           int cap, const float* sink, int gate_per_head, cudaStream_t stream);
 int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq, const int* cu,
                             const int* pos0, const int* slot, int n_tok, int GD, int GE, int cap, int act_fp32,
                             cudaStream_t stream);
@@ -354,23 +364,44 @@ int llark_seq_group_rmsnorm(const float* x, const int* rows, const float* add_ve
 /* x_out = x + (y + sum_k wts[t, k] * z[pos_of[t * top + k]]); top = 0: x + y */
 int llark_seq_residual_combine(const float* x, const float* y, const float* z, const int* pos_of, const float* wts,
                                int top, float* x_out, int n_tok, int C, cudaStream_t stream);
-/* out[t, c] = act(sum_j w[c, j] * src[t - taps + 1 + j, c]) over n_ch columns of a strided fp32 matrix (src points at the
+/* out[t, c] = act(bias[c] + sum_j w[c, j] * src[t - taps + 1 + j, c]) (bias optional) over n_ch columns of a strided fp32 matrix (src points at the
  * first column); carry fp32 [slots, taps-1, n_ch] holds each request's last inputs and is refreshed */
 int llark_seq_conv_act(const float* src, long long ld, const float* w, float* carry, const int* tok_seq, const int* cu,
-                       const int* slot, float* out, int n_tok, int n_seq, int n_ch, int taps, int silu,
+                       const int* slot, float* out, int n_tok, int n_seq, int n_ch, int taps, int silu, const float* bias,
                        cudaStream_t stream);
 /* the five vectors {q, z, d, p1, p2} [n_tok, H, 5, D] of the delta-rule scan; rule 0: gated delta rule, rule 1:
- * generalized delta rule (see csrc/seq_delta.cu) */
+ * generalized delta rule, rule 2: gated delta rule with one decay per head, rule 3: state-space rule S <- a S + dt B x^T,
+ * y = S^T C (see csrc/seq_delta.cu) */
 int llark_seq_delta_prep(int rule, const float* q, long long q_ld, const float* k, long long k_ld, const float* dec,
                          long long dec_ld, const float* dec_bias, const float* rate_log, const float* mix,
                          long long mix_ld, float* vec, int n_tok, int H, int G, int D, float unit_eps,
                          cudaStream_t stream);
-/* S[:, e] = d S[:, e] + p1 (z . S[:, e]) + p2 v[e], o[e] = q . S[:, e] per token; state fp32 [slots, H, D, E] */
+/* S[:, e] = d S[:, e] + p1 (z . S[:, e]) + p2 v[e], o[e] = q . S[:, e] per token; state fp32 [slots, H, D, E];
+ * correct = 0: the p1 term is skipped (rules whose p1 is zero) */
 int llark_seq_delta_scan(const float* vec, const float* v, long long v_ld, float* state, float* o, const int* cu,
-                         const int* slot, int n_seq, int n_tok, int H, int D, int E, cudaStream_t stream);
-/* per-head RMS norm of x fp32 [n_tok, H, E], times w ([E] shared or [H, E]), times sigmoid(gate) -> ACT */
+                         const int* slot, int n_seq, int n_tok, int H, int D, int E, int correct, cudaStream_t stream);
+/* per-head RMS norm of x fp32 [n_tok, H, E], times w ([E] shared or [H, E]), times sigmoid(gate) (gate_silu: times
+ * gate * sigmoid(gate)) -> ACT */
 int llark_seq_head_norm_gate(const float* x, const float* w, int w_per_head, const float* gate, long long gate_ld,
-                             void* out, long long n_tok, int H, int E, float eps, int act_fp32, cudaStream_t stream);
+                             void* out, long long n_tok, int H, int E, float eps, int gate_silu, int act_fp32,
+                             cudaStream_t stream);
+/* read-out of a state-space mixer: y = (o + skip[h] * xin) * silu(gate) over the H * E inner channels, RMS norm of each
+ * of `groups` equal consecutive parts, times w fp32 [H * E] -> ACT [n_tok, H * E] */
+int llark_seq_skip_gate_group_norm(const float* o, const float* xin, long long x_ld, const float* skip, const float* gate,
+                                   long long gate_ld, const float* w, void* out, long long n_tok, int H, int E, int groups,
+                                   float eps, int act_fp32, cudaStream_t stream);
+/* Norm after the residual sum: x_out = rmsnorm(alpha * x + f) * w, f = branch_scale * (b1 + b2) + sum_k wts[t, k] * e_k
+ * with b_i = y_i, or rmsnorm(y_i) * w_i when w_i is given (y2 optional), and e_k = row pos_of[t * top + k] of z, or x
+ * itself when ids[t * top + k] >= n_real (top = 0: no such terms). x_act (optional) gets x_out in the activation dtype. */
+int llark_seq_post_norm(const float* x, float alpha, const float* y1, const float* w1, const float* y2, const float* w2,
+                        float branch_scale, const float* z, const int* pos_of, const float* wts, const int* ids, int top,
+                        int n_real, const float* w, float* x_out, void* x_act, long long rows, int C, float eps,
+                        int act_fp32, cudaStream_t stream);
+/* act = g' * sigmoid(slope * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu = [g | u] rows */
+int llark_seq_glu_clamped(const void* gu, void* act, long long rows, int ff, float limit, float slope, int act_fp32,
+                          cudaStream_t stream);
+/* z <- cap * tanh(z * scale / cap) in place (cap <= 0: z * scale) */
+int llark_seq_logit_cap(float* z, long long n, float scale, float cap, cudaStream_t stream);
 /* latent attention: normed latent and rotated shared key part -> ckr ACT [n_tok, R + P] (and the ring row of the
  * token's position when ring != NULL), rotated query parts -> qf ACT [n_tok, H, R + P] columns R.. */
 int llark_seq_latent_prep(const float* q, long long q_ld, const float* lat, long long lat_ld, const float* norm_w,
@@ -390,10 +421,15 @@ int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, lo
 /* routed mixture of experts (see csrc/seq_moe.cu) */
 int llark_seq_moe_route(const float* logits, long long ld, int* ids, float* wts, int n_tok, int n_exp, int n_groups,
                         int keep, int top, float scale, cudaStream_t stream);
+/* softmax scores; choice on score + correction (optional) within the `keep` groups whose best choice score is largest;
+ * weights = the chosen experts' plain scores * scale */
+int llark_seq_moe_route_bias(const float* logits, long long ld, const float* correction, int* ids, float* wts, int n_tok,
+                             int n_exp, int n_groups, int keep, int top, float scale, cudaStream_t stream);
 int llark_seq_moe_tile_rows(void);
-/* meta[0] = number of 64-row tiles; with tiles256: 256-row tiles for llark_gemm_segments, their number in meta[1] */
-int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta, int* seg_off,
-                       int* tiles256, cudaStream_t stream);
+/* meta[0] = number of 64-row tiles; with tiles256: 256-row tiles for llark_gemm_segments, their number in meta[1];
+ * experts >= n_real have no weights and get no tiles */
+int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int n_real, int* perm, int* pos_of, int* tiles, int* meta,
+                       int* seg_off, int* tiles256, cudaStream_t stream);
 /* xs[p] = x[perm[p] / top] (rows in sorted order); act = silu(gu[:, :ff]) * gu[:, ff:] */
 int llark_seq_moe_gather(const void* x, long long ldx, const int* perm, int top, void* xs, int n_ent, int C, int act_fp32,
                          cudaStream_t stream);

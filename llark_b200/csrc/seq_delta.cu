@@ -44,14 +44,14 @@ template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p,
 __global__ void conv_act_kernel(const float* __restrict__ src, long long ld, const float* __restrict__ w,
                                 float* __restrict__ carry, const int* __restrict__ tok_seq, const int* __restrict__ cu,
                                 const int* __restrict__ slot, float* __restrict__ out, int n_ch, int taps, int silu,
-                                int inline_carry) {
+                                int inline_carry, const float* __restrict__ bias) {
     const int t = blockIdx.x;
     const int b = tok_seq[t];
     const int local = t - cu[b];
     float* cr = carry + (long long)slot[b] * (taps - 1) * n_ch;
     for (int c = threadIdx.x; c < n_ch; c += blockDim.x) {
         const float cur = src[(long long)t * ld + c];
-        float acc = 0.f;
+        float acc = bias ? bias[c] : 0.f;
         for (int j = 0; j < taps - 1; ++j) {
             const int s = local - taps + 1 + j;
             const float v = s >= 0 ? src[(long long)(t - local + s) * ld + c] : cr[(long long)(taps - 1 + s) * n_ch + c];
@@ -73,13 +73,14 @@ template <int TAPS, int TB>
 __global__ void conv_act_rows_kernel(const float* __restrict__ src, long long ld, const float* __restrict__ w,
                                      const float* __restrict__ carry, const int* __restrict__ tok_seq,
                                      const int* __restrict__ cu, const int* __restrict__ slot, float* __restrict__ out,
-                                     int n_tok, int n_ch, int silu) {
+                                     int n_tok, int n_ch, int silu, const float* __restrict__ bias) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= n_ch) return;
     const int t0 = blockIdx.x * TB;
     float wr[TAPS], win[TAPS > 1 ? TAPS - 1 : 1];
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) wr[j] = w[(long long)c * TAPS + j];
+    const float b0 = bias ? bias[c] : 0.f;
     for (int i = 0; i < TB && t0 + i < n_tok; ++i) {
         const int t = t0 + i;
         const int b = tok_seq[t];
@@ -93,7 +94,7 @@ __global__ void conv_act_rows_kernel(const float* __restrict__ src, long long ld
             }
         }
         const float cur = src[(long long)t * ld + c];
-        float acc = 0.f;
+        float acc = b0;
 #pragma unroll
         for (int j = 0; j < TAPS - 1; ++j) acc = fmaf(wr[j], win[j], acc);
         acc = fmaf(wr[TAPS - 1], cur, acc);
@@ -123,6 +124,10 @@ __global__ void conv_carry_kernel(const float* __restrict__ src, long long ld, f
 //                               decay, + dec_bias [H*D]; rate_log [H]; mix [n_tok, H] pre-activation of beta
 //   rule 1 (generalized delta): q = r, k [n_tok, H, D]; dec [n_tok, H*D] (bias included); mix [n_tok, H*D] pre-activation
 //                               of the removal rate
+//   rule 2 (gated delta, one decay per head): as rule 0 with dec [n_tok, H], dec_bias [H]
+//   rule 3 (state space):       S <- a S + dt B x^T, y = S^T C with a = exp(-exp(rate_log_h) dt), dt = softplus(dec +
+//                               dec_bias) per head: q = C, k = B [n_tok, G, D] (D = state size), dec [n_tok, H]; the
+//                               vectors are q = C, z = 0, d = a, p1 = 0, p2 = dt B (the scan may skip the correction)
 __global__ void delta_prep_kernel(int rule, const float* __restrict__ q, long long q_ld, const float* __restrict__ k,
                                   long long k_ld, const float* __restrict__ dec, long long dec_ld,
                                   const float* __restrict__ dec_bias, const float* __restrict__ rate_log,
@@ -145,7 +150,29 @@ __global__ void delta_prep_kernel(int rule, const float* __restrict__ q, long lo
     sk = warp_sum(sk);
     sq = warp_sum(sq);
     const float rk = 1.0f / sqrtf(sk + unit_eps);
-    if (rule == 0) {
+    if (rule == 3) {
+        const float dt = softplusf_(dec[t * dec_ld + h] + dec_bias[h]);
+        const float a = expf(-expf(rate_log[h]) * dt);
+        for (int d = lane; d < D; d += 32) {
+            o[d] = qr[d];
+            o[D + d] = 0.f;
+            o[2 * D + d] = a;
+            o[3 * D + d] = 0.f;
+            o[4 * D + d] = dt * kr[d];
+        }
+    } else if (rule == 2) {
+        const float rq = 1.0f / sqrtf(sq + unit_eps) / sqrtf((float)D);
+        const float beta = sigmoidf_(mix[t * mix_ld + h]);
+        const float gd = expf(-expf(rate_log[h]) * softplusf_(dec[t * dec_ld + h] + dec_bias[h]));
+        for (int d = lane; d < D; d += 32) {
+            const float kh = kr[d] * rk;
+            o[d] = qr[d] * rq;
+            o[D + d] = kh * gd;
+            o[2 * D + d] = gd;
+            o[3 * D + d] = -beta * kh;
+            o[4 * D + d] = beta * kh;
+        }
+    } else if (rule == 0) {
         const float rq = 1.0f / sqrtf(sq + unit_eps) / sqrtf((float)D);
         const float beta = sigmoidf_(mix[t * mix_ld + h]);
         const float rate = expf(rate_log[h]);
@@ -188,7 +215,8 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int DPT, int CPT, int R>
+// CORR = false: rules without the correction term (p1 = 0, as the state-space rule) skip the z . S pass.
+template <int DPT, int CPT, int R, bool CORR>
 __global__ void __launch_bounds__(256, 1)
 delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, long long v_ld, float* __restrict__ state,
                   float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slot, int H, int D, int E,
@@ -268,23 +296,25 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
             float zs[CPT], zt[CPT];
 #pragma unroll
             for (int c = 0; c < CPT; ++c) zs[c] = zt[c] = 0.f;
+            if (CORR) {
 #pragma unroll
-            for (int i = 0; i < DPT / 4; ++i) {
-                const float4 z = pz[R * i];
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 z = pz[R * i];
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) {
-                    zs[c] = fmaf(z.x, S[c][4 * i], zs[c]);
-                    zt[c] = fmaf(z.y, S[c][4 * i + 1], zt[c]);
-                    zs[c] = fmaf(z.z, S[c][4 * i + 2], zs[c]);
-                    zt[c] = fmaf(z.w, S[c][4 * i + 3], zt[c]);
+                    for (int c = 0; c < CPT; ++c) {
+                        zs[c] = fmaf(z.x, S[c][4 * i], zs[c]);
+                        zt[c] = fmaf(z.y, S[c][4 * i + 1], zt[c]);
+                        zs[c] = fmaf(z.z, S[c][4 * i + 2], zs[c]);
+                        zt[c] = fmaf(z.w, S[c][4 * i + 3], zt[c]);
+                    }
                 }
-            }
 #pragma unroll
-            for (int c = 0; c < CPT; ++c) zs[c] += zt[c];
+                for (int c = 0; c < CPT; ++c) zs[c] += zt[c];
 #pragma unroll
-            for (int m = 1; m < R; m <<= 1) {
+                for (int m = 1; m < R; m <<= 1) {
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) zs[c] += __shfl_xor_sync(0xffffffffu, zs[c], m);
+                    for (int c = 0; c < CPT; ++c) zs[c] += __shfl_xor_sync(0xffffffffu, zs[c], m);
+                }
             }
             float vv[CPT], os[CPT], ot[CPT];
 #pragma unroll
@@ -294,13 +324,21 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
             }
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
-                const float4 dd = pd[R * i], a = p1[R * i], w2 = p2[R * i], qq = pq[R * i];
+                const float4 dd = pd[R * i], w2 = p2[R * i], qq = pq[R * i];
+                const float4 a = CORR ? p1[R * i] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) {
-                    S[c][4 * i] = fmaf(w2.x, vv[c], fmaf(a.x, zs[c], dd.x * S[c][4 * i]));
-                    S[c][4 * i + 1] = fmaf(w2.y, vv[c], fmaf(a.y, zs[c], dd.y * S[c][4 * i + 1]));
-                    S[c][4 * i + 2] = fmaf(w2.z, vv[c], fmaf(a.z, zs[c], dd.z * S[c][4 * i + 2]));
-                    S[c][4 * i + 3] = fmaf(w2.w, vv[c], fmaf(a.w, zs[c], dd.w * S[c][4 * i + 3]));
+                    if (CORR) {
+                        S[c][4 * i] = fmaf(w2.x, vv[c], fmaf(a.x, zs[c], dd.x * S[c][4 * i]));
+                        S[c][4 * i + 1] = fmaf(w2.y, vv[c], fmaf(a.y, zs[c], dd.y * S[c][4 * i + 1]));
+                        S[c][4 * i + 2] = fmaf(w2.z, vv[c], fmaf(a.z, zs[c], dd.z * S[c][4 * i + 2]));
+                        S[c][4 * i + 3] = fmaf(w2.w, vv[c], fmaf(a.w, zs[c], dd.w * S[c][4 * i + 3]));
+                    } else {
+                        S[c][4 * i] = fmaf(w2.x, vv[c], dd.x * S[c][4 * i]);
+                        S[c][4 * i + 1] = fmaf(w2.y, vv[c], dd.y * S[c][4 * i + 1]);
+                        S[c][4 * i + 2] = fmaf(w2.z, vv[c], dd.z * S[c][4 * i + 2]);
+                        S[c][4 * i + 3] = fmaf(w2.w, vv[c], dd.w * S[c][4 * i + 3]);
+                    }
                     os[c] = fmaf(qq.x, S[c][4 * i], os[c]);
                     ot[c] = fmaf(qq.y, S[c][4 * i + 1], ot[c]);
                     os[c] = fmaf(qq.z, S[c][4 * i + 2], os[c]);
@@ -333,11 +371,11 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
 }
 
 // ------------------------------------------------------------------------------------------------ read-out norm + gate
-// Warp per (token, head): y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate)
+// Warp per (token, head): y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate)   (gate_silu: * gate * sigmoid(gate))
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, int w_per_head,
                                       const float* __restrict__ gate, long long gate_ld, T* __restrict__ out,
-                                      long long n_items, int H, int E, float eps) {
+                                      long long n_items, int H, int E, float eps, int gate_silu) {
     const int lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= n_items) return;
@@ -351,8 +389,44 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ x, const float* 
     const float* wr = w + (w_per_head ? (long long)h * E : 0);
     for (int e = lane; e < E; e += 32) {
         float y = xr[e] * r * wr[e];
-        if (gate) y *= sigmoidf_(gate[t * gate_ld + (long long)h * E + e]);
+        if (gate) {
+            const float gv = gate[t * gate_ld + (long long)h * E + e];
+            y *= gate_silu ? gv * sigmoidf_(gv) : sigmoidf_(gv);
+        }
         stf(out + item * E + e, y);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ skip, gate, grouped norm
+// Read-out of a state-space mixer: y = (o + skip_h * xin) * silu(gate) over the H * E inner channels of a token, then an RMS
+// norm of each of `groups` equal consecutive parts by its own root mean square, times w [H * E]. Block per (token, part).
+template <typename T>
+__global__ void skip_gate_group_norm_kernel(const float* __restrict__ o, const float* __restrict__ xin, long long x_ld,
+                                            const float* __restrict__ skip, const float* __restrict__ gate,
+                                            long long gate_ld, const float* __restrict__ w, T* __restrict__ out, int H,
+                                            int E, int groups, float eps) {
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const int inner = H * E, per = inner / groups, c0 = blockIdx.y * per;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int c = c0 + i;
+        const float gv = gate[t * gate_ld + c];
+        const float y = (o[t * inner + c] + skip[c / E] * xin[t * x_ld + c]) * (gv * sigmoidf_(gv));
+        ss = fmaf(y, y, ss);
+    }
+    ss = warp_sum(ss);
+    const int wi = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) red[wi] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)per + eps);
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int c = c0 + i;
+        const float gv = gate[t * gate_ld + c];
+        const float y = (o[t * inner + c] + skip[c / E] * xin[t * x_ld + c]) * (gv * sigmoidf_(gv));
+        stf(out + t * inner + c, y * r * w[c]);
     }
 }
 
@@ -364,7 +438,7 @@ using namespace llark::delta;
 
 extern "C" int llark_seq_conv_act(const float* src, long long ld, const float* w, float* carry, const int* tok_seq,
                                   const int* cu, const int* slot, float* out, int n_tok, int n_seq, int n_ch, int taps,
-                                  int silu, cudaStream_t st) {
+                                  int silu, const float* bias, cudaStream_t st) {
     if (n_tok <= 0 || n_seq <= 0 || n_ch <= 0 || taps < 1 || !src || !w || !out || ld < n_ch || (taps > 1 && !carry) ||
         !tok_seq || !cu || !slot)
         return LLARK_EINVAL;
@@ -375,13 +449,17 @@ extern "C" int llark_seq_conv_act(const float* src, long long ld, const float* w
         constexpr int TB = 16;
         dim3 grid((n_tok + TB - 1) / TB, (n_ch + 127) / 128);
         if (taps == 2)
-            conv_act_rows_kernel<2, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu);
+            conv_act_rows_kernel<2, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu,
+                                                              bias);
         else if (taps == 3)
-            conv_act_rows_kernel<3, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu);
+            conv_act_rows_kernel<3, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu,
+                                                              bias);
         else
-            conv_act_rows_kernel<4, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu);
+            conv_act_rows_kernel<4, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu,
+                                                              bias);
     } else {
-        conv_act_kernel<<<n_tok, th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu, inline_carry);
+        conv_act_kernel<<<n_tok, th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu, inline_carry,
+                                              bias);
     }
     int rc = check_launch();
     if (rc != LLARK_OK || inline_carry || taps == 1) return rc;
@@ -393,8 +471,10 @@ extern "C" int llark_seq_delta_prep(int rule, const float* q, long long q_ld, co
                                     const float* dec, long long dec_ld, const float* dec_bias, const float* rate_log,
                                     const float* mix, long long mix_ld, float* vec, int n_tok, int H, int G, int D,
                                     float unit_eps, cudaStream_t st) {
-    if (n_tok <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || !q || !k || !dec || !mix || !vec) return LLARK_EINVAL;
-    if (rule == 0 ? (!dec_bias || !rate_log) : (rule != 1 || G != H)) return LLARK_EINVAL;
+    if (n_tok <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || !q || !k || !dec || (!mix && rule != 3) || !vec)
+        return LLARK_EINVAL;
+    if (rule < 0 || rule > 3) return LLARK_EINVAL;
+    if (rule == 1 ? G != H : (!dec_bias || !rate_log)) return LLARK_EINVAL;
     const long long items = (long long)n_tok * H;
     delta_prep_kernel<<<(unsigned)((items + 3) / 4), 128, 0, st>>>(rule, q, q_ld, k, k_ld, dec, dec_ld, dec_bias, rate_log,
                                                                    mix, mix_ld, vec, n_tok, H, G, D, unit_eps);
@@ -403,7 +483,7 @@ extern "C" int llark_seq_delta_prep(int rule, const float* q, long long q_ld, co
 
 extern "C" int llark_seq_delta_scan(const float* vec, const float* v, long long v_ld, float* state, float* o,
                                     const int* cu, const int* slot, int n_seq, int n_tok, int H, int D, int E,
-                                    cudaStream_t st) {
+                                    int correct, cudaStream_t st) {
     if (n_seq <= 0 || n_tok < n_seq || H <= 0 || D <= 0 || E <= 0 || !vec || !v || !state || !o || !cu || !slot)
         return LLARK_EINVAL;
     // 16 rows of a column per thread (short dependent chains) while a column then still fits one warp, 32 rows for the
@@ -435,7 +515,12 @@ extern "C" int llark_seq_delta_scan(const float* vec, const float* v, long long 
     const size_t smem = sizeof(float) * 2 * (size_t)ts * (5 * dpt * R + cols);
     dim3 grid((E + cols - 1) / cols, H, n_seq);
 #define LLARK_DSCAN(DPT_, CPT_, R_)                                                                                   \
-    delta_scan_kernel<DPT_, CPT_, R_><<<grid, threads, smem, st>>>(vec, v, v_ld, state, o, cu, slot, H, D, E, cols, ts)
+    if (correct)                                                                                                      \
+        delta_scan_kernel<DPT_, CPT_, R_, true><<<grid, threads, smem, st>>>(vec, v, v_ld, state, o, cu, slot, H, D, E, \
+                                                                             cols, ts);                               \
+    else                                                                                                              \
+        delta_scan_kernel<DPT_, CPT_, R_, false><<<grid, threads, smem, st>>>(vec, v, v_ld, state, o, cu, slot, H, D,   \
+                                                                              E, cols, ts)
 #define LLARK_DSCAN_R(DPT_, CPT_)                                                                                     \
     switch (R) {                                                                                                      \
         case 1: LLARK_DSCAN(DPT_, CPT_, 1); break;                                                                    \
@@ -461,14 +546,34 @@ extern "C" int llark_seq_delta_scan(const float* vec, const float* v, long long 
 
 extern "C" int llark_seq_head_norm_gate(const float* x, const float* w, int w_per_head, const float* gate,
                                         long long gate_ld, void* out, long long n_tok, int H, int E, float eps,
-                                        int act_fp32, cudaStream_t st) {
+                                        int gate_silu, int act_fp32, cudaStream_t st) {
     if (n_tok <= 0 || H <= 0 || E <= 0 || !x || !w || !out) return LLARK_EINVAL;
     const long long items = n_tok * H;
     const unsigned grid = (unsigned)((items + 3) / 4);
     if (act_fp32)
-        head_norm_gate_kernel<float><<<grid, 128, 0, st>>>(x, w, w_per_head, gate, gate_ld, (float*)out, items, H, E, eps);
+        head_norm_gate_kernel<float><<<grid, 128, 0, st>>>(x, w, w_per_head, gate, gate_ld, (float*)out, items, H, E, eps,
+                                                           gate_silu);
     else
         head_norm_gate_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(x, w, w_per_head, gate, gate_ld, (__nv_bfloat16*)out,
-                                                                   items, H, E, eps);
+                                                                   items, H, E, eps, gate_silu);
+    return check_launch();
+}
+
+extern "C" int llark_seq_skip_gate_group_norm(const float* o, const float* xin, long long x_ld, const float* skip,
+                                              const float* gate, long long gate_ld, const float* w, void* out,
+                                              long long n_tok, int H, int E, int groups, float eps, int act_fp32,
+                                              cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || E <= 0 || groups <= 0 || ((H * E) % groups) || !o || !xin || !skip || !gate || !w || !out)
+        return LLARK_EINVAL;
+    const int per = H * E / groups;
+    int th = 32;
+    while (th < per && th < 256) th <<= 1;
+    dim3 grid((unsigned)n_tok, groups);
+    if (act_fp32)
+        skip_gate_group_norm_kernel<float><<<grid, th, 0, st>>>(o, xin, x_ld, skip, gate, gate_ld, w, (float*)out, H, E,
+                                                                groups, eps);
+    else
+        skip_gate_group_norm_kernel<__nv_bfloat16><<<grid, th, 0, st>>>(o, xin, x_ld, skip, gate, gate_ld, w,
+                                                                        (__nv_bfloat16*)out, H, E, groups, eps);
     return check_launch();
 }

@@ -37,14 +37,16 @@ template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p,
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // ------------------------------------------------------------------------------------------------ q / k head norm
-// src [n_tok, ld] fp32 with q heads at column q_off and k heads at k_off. Warp per (token, head).
+// src [n_tok, ld] fp32 with q heads at column q_off, k heads at k_off and the values' source at v_off (E per key / value
+// head; v_off = k_off with E = D makes the un-normed keys the values). Warp per (token, head). temp_every > 0: the query
+// is also multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position p of its sequence.
 template <typename T>
-__global__ void qk_headnorm_kernel(const float* __restrict__ src, long long ld, int q_off, int k_off,
+__global__ void qk_headnorm_kernel(const float* __restrict__ src, long long ld, int q_off, int k_off, int v_off,
                                    const float* __restrict__ wq, const float* __restrict__ wk, T* __restrict__ qn,
                                    T* __restrict__ kn, T* __restrict__ vraw, T* __restrict__ kring, T* __restrict__ vring,
                                    const int* __restrict__ tok_seq, const int* __restrict__ cu,
-                                   const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D,
-                                   int cap, float eps) {
+                                   const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D, int E,
+                                   int cap, float eps, float temp_coef, int temp_every) {
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int hh = warp; hh < H + G; hh += nw) {
@@ -54,30 +56,36 @@ __global__ void qk_headnorm_kernel(const float* __restrict__ src, long long ld, 
         float ss = 0.f;
         for (int d = lane; d < D; d += 32) ss = fmaf(s[d], s[d], ss);
         ss = warp_sum(ss);
-        const float r = 1.0f / sqrtf(ss / (float)D + eps);
+        float r = 1.0f / sqrtf(ss / (float)D + eps);
         const float* w = is_q ? wq : wk;
         if (is_q) {
+            if (temp_every > 0) {
+                const int b = tok_seq[t];
+                const long long p = pos0[b] + (t - cu[b]);
+                r *= 1.0f + temp_coef * logf((float)((p + 1) / temp_every) + 1.0f);
+            }
             T* o = qn + ((long long)t * H + head) * D;
             for (int d = lane; d < D; d += 32) stf(o + d, s[d] * r * w[d]);
         } else {
+            const float* sv = src + (long long)t * ld + v_off + head * E;
             T* o = kn + ((long long)t * G + head) * D;
-            T* ov = vraw + ((long long)t * G + head) * D;
+            T* ov = vraw + ((long long)t * G + head) * E;
             T *rk = nullptr, *rv = nullptr;
             if (kring) {  // one token per request: the entry it replaces is already outside the window
                 const int b = tok_seq[t];
                 const long long p = pos0[b] + (t - cu[b]);
                 const long long e = ((long long)slot[b] * cap + (p % cap)) * G + head;
                 rk = kring + e * D;
-                rv = vring + e * D;
+                rv = vring + e * E;
             }
             for (int d = lane; d < D; d += 32) {
                 const float kv = s[d] * r * w[d];
                 stf(o + d, kv);
-                stf(ov + d, s[d]);
-                if (rk) {
-                    stf(rk + d, kv);
-                    stf(rv + d, s[d]);
-                }
+                if (rk) stf(rk + d, kv);
+            }
+            for (int d = lane; d < E; d += 32) {
+                stf(ov + d, sv[d]);
+                if (rv) stf(rv + d, sv[d]);
             }
         }
     }
@@ -127,7 +135,8 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
                                 long long gate_ld, const float* __restrict__ scale_h, T* __restrict__ out,
                                 const int* __restrict__ tok_seq, const int* __restrict__ cu,
                                 const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D, int E,
-                                int window, int cap, int from_ring_only) {
+                                int window, int cap, int from_ring_only, const float* __restrict__ sink,
+                                int gate_per_head) {
     extern __shared__ float sm[];
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* sq = sm;                      // [D]
@@ -220,16 +229,16 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
         if (e < E) sacc[warp * E + e] = acc[i];
     }
     __syncthreads();
-    float mm = -INFINITY;
+    float mm = sink ? sink[h] : -INFINITY;  // a sink is one more term exp(sink_h) of the denominator, with no value
     for (int w = 0; w < nw; ++w) mm = fmaxf(mm, sm_m[w]);
-    float lt = 0.f;
+    float lt = sink ? expf(sink[h] - mm) : 0.f;
     for (int w = 0; w < nw; ++w) lt += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * expf(sm_m[w] - mm);
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < nw; ++w)
             if (sm_m[w] != -INFINITY) o = fmaf(sacc[w * E + e], expf(sm_m[w] - mm), o);
         o /= lt;
-        if (gate) o *= sigmoidf_(gate[(long long)t * gate_ld + h * E + e]);
+        if (gate) o *= sigmoidf_(gate[(long long)t * gate_ld + (gate_per_head ? h : h * E + e)]);
         stf(out + ((long long)t * H + h) * E + e, o);
     }
 }
@@ -441,29 +450,50 @@ using namespace llark;
 using namespace llark::seqmix;
 typedef __nv_bfloat16 bf16_t;
 
+static int launch_headnorm(const float* src, long long ld, int q_off, int k_off, int v_off, const float* wq,
+                           const float* wk, void* qn, void* kn, void* vv, void* kring, void* vring, const int* tok_seq,
+                           const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int cap,
+                           float eps, float temp_coef, int temp_every, int act_fp32, cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || G <= 0 || D <= 0 || E <= 0 || !src || !wq || !wk || !qn || !kn || !vv) return LLARK_EINVAL;
+    if (kring && (!vring || cap <= 0 || !tok_seq || !cu || !pos0 || !slot)) return LLARK_EINVAL;
+    if (temp_every > 0 && (!tok_seq || !cu || !pos0)) return LLARK_EINVAL;
+    int warps = H + G < 8 ? H + G : 8;
+    if (act_fp32)
+        qk_headnorm_kernel<float><<<n_tok, warps * 32, 0, st>>>(src, ld, q_off, k_off, v_off, wq, wk, (float*)qn,
+                                                                (float*)kn, (float*)vv, (float*)kring, (float*)vring,
+                                                                tok_seq, cu, pos0, slot, H, G, D, E, cap, eps, temp_coef,
+                                                                temp_every);
+    else
+        qk_headnorm_kernel<bf16_t><<<n_tok, warps * 32, 0, st>>>(src, ld, q_off, k_off, v_off, wq, wk, (bf16_t*)qn,
+                                                                 (bf16_t*)kn, (bf16_t*)vv, (bf16_t*)kring, (bf16_t*)vring,
+                                                                 tok_seq, cu, pos0, slot, H, G, D, E, cap, eps, temp_coef,
+                                                                 temp_every);
+    return check_launch();
+}
+
 extern "C" int llark_seq_qk_headnorm(const float* src, long long ld, int q_off, int k_off, const float* wq,
                                      const float* wk, void* qn, void* kn, void* vraw, void* kring, void* vring,
                                      const int* tok_seq, const int* cu, const int* pos0, const int* slot, int n_tok, int H,
                                      int G, int D, int cap, float eps, int act_fp32, cudaStream_t st) {
-    if (n_tok <= 0 || H <= 0 || G <= 0 || D <= 0 || !src || !wq || !wk || !qn || !kn || !vraw) return LLARK_EINVAL;
-    if (kring && (!vring || cap <= 0 || !tok_seq || !cu || !pos0 || !slot)) return LLARK_EINVAL;
-    int warps = H + G < 8 ? H + G : 8;
-    if (act_fp32)
-        qk_headnorm_kernel<float><<<n_tok, warps * 32, 0, st>>>(src, ld, q_off, k_off, wq, wk, (float*)qn, (float*)kn,
-                                                                (float*)vraw, (float*)kring, (float*)vring, tok_seq, cu,
-                                                                pos0, slot, H, G, D, cap, eps);
-    else
-        qk_headnorm_kernel<bf16_t><<<n_tok, warps * 32, 0, st>>>(src, ld, q_off, k_off, wq, wk, (bf16_t*)qn, (bf16_t*)kn,
-                                                                 (bf16_t*)vraw, (bf16_t*)kring, (bf16_t*)vring, tok_seq,
-                                                                 cu, pos0, slot, H, G, D, cap, eps);
-    return check_launch();
+    return launch_headnorm(src, ld, q_off, k_off, k_off, wq, wk, qn, kn, vraw, kring, vring, tok_seq, cu, pos0, slot, n_tok,
+                           H, G, D, D, cap, eps, 0.f, 0, act_fp32, st);
+}
+
+extern "C" int llark_seq_qkv_headnorm(const float* src, long long ld, int q_off, int k_off, int v_off, const float* wq,
+                                      const float* wk, void* qn, void* kn, void* vv, void* kring, void* vring,
+                                      const int* tok_seq, const int* cu, const int* pos0, const int* slot, int n_tok,
+                                      int H, int G, int D, int E, int cap, float eps, float temp_coef, int temp_every,
+                                      int act_fp32, cudaStream_t st) {
+    if (temp_every < 0) return LLARK_EINVAL;
+    return launch_headnorm(src, ld, q_off, k_off, v_off, wq, wk, qn, kn, vv, kring, vring, tok_seq, cu, pos0, slot, n_tok,
+                           H, G, D, E, cap, eps, temp_coef, temp_every, act_fp32, st);
 }
 
 template <typename T>
 static int launch_swa(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                       const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
                       const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
-                      int cap, int from_ring_only, cudaStream_t st) {
+                      int cap, int from_ring_only, const float* sink, int gate_per_head, cudaStream_t st) {
     int nw = 1;
     while (nw < 8 && nw * 64 < window) nw <<= 1;  // two tiles per warp before another warp pays off
     const size_t smem = sizeof(float) * (size_t)(D + nw * 32 + 2 * nw + nw * E);
@@ -472,7 +502,8 @@ static int launch_swa(const void* qn, const void* kn, const void* vv, const void
 #define LLARK_SWA(DPL)                                                                                              \
     swa_attn_kernel<T, DPL><<<grid, nw * 32, smem, st>>>((const T*)qn, (const T*)kn, (const T*)vv, (const T*)kring, \
                                                          (const T*)vring, gate, gate_ld, scale_h, (T*)out, tok_seq, \
-                                                         cu, pos0, slot, H, G, D, E, window, cap, from_ring_only)
+                                                         cu, pos0, slot, H, G, D, E, window, cap, from_ring_only, \
+                                                         sink, gate_per_head)
     if (dpl <= 1) LLARK_SWA(1);
     else if (dpl <= 2) LLARK_SWA(2);
     else if (dpl <= 4) LLARK_SWA(4);
@@ -487,17 +518,17 @@ static int launch_swa(const void* qn, const void* kn, const void* vv, const void
 extern "C" int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                                   const float* gate, long long gate_ld, const float* scale_h, void* out,
                                   const int* tok_seq, const int* cu, const int* pos0, const int* slot, int n_tok, int H,
-                                  int G, int D, int E, int window, int cap, int from_ring_only, int act_fp32,
-                                  cudaStream_t st) {
+                                  int G, int D, int E, int window, int cap, int from_ring_only, const float* sink,
+                                  int gate_per_head, int act_fp32, cudaStream_t st) {
     if (n_tok <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || E <= 0 || window <= 0 || cap <= 0 || !qn || !kring ||
         !vring || !scale_h || !out || !tok_seq || !cu || !pos0 || !slot)
         return LLARK_EINVAL;
     if (!from_ring_only && (!kn || !vv)) return LLARK_EINVAL;
     if ((size_t)(D + 8 * 32 + 16 + 8 * E) * sizeof(float) > 48 * 1024) return LLARK_EINVAL;
     return act_fp32 ? launch_swa<float>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, tok_seq, cu, pos0, slot,
-                                        n_tok, H, G, D, E, window, cap, from_ring_only, st)
+                                        n_tok, H, G, D, E, window, cap, from_ring_only, sink, gate_per_head, st)
                     : launch_swa<bf16_t>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, tok_seq, cu, pos0, slot,
-                                         n_tok, H, G, D, E, window, cap, from_ring_only, st);
+                                         n_tok, H, G, D, E, window, cap, from_ring_only, sink, gate_per_head, st);
 }
 
 extern "C" int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq,

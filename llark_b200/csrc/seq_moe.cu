@@ -10,6 +10,11 @@
 //   llark_seq_moe_route     scores = sigmoid(logits) fp32; experts form `n_groups` groups of neighbours, a group's score
 //                           is the sum of its two best, only experts of the best `keep` groups can be chosen; the `top`
 //                           best of those; weights = their scores / (sum + 1e-20) * scale
+//   llark_seq_moe_route_bias  scores = softmax(logits) fp32 over all router outputs; the CHOICE is made on score +
+//                           correction (which may be negative), a group's score is its best choice score, experts outside
+//                           the best `keep` groups cannot be chosen; weights = the chosen experts' plain scores * scale,
+//                           not renormalised. Router outputs >= n_real are experts without weights that hand their input
+//                           through: the sort leaves them out of the tile lists, the residual kernel adds the input.
 //   llark_seq_moe_sort      entries -> perm (sorted by expert), pos_of (inverse), tiles (expert, first row, rows)
 //   llark_seq_moe_up        act[pos] = silu(W_gate,e x) * (W_up,e x)     x = the entry's token row
 //   llark_seq_moe_down      z[pos]   = W_down,e act[pos]                 fp32
@@ -118,9 +123,93 @@ __global__ void route_kernel(const float* __restrict__ logits, long long ld, int
     }
 }
 
+// Warp per token. s = plain scores, c = choice scores (-inf once taken or shut out). Ties go to the lower number.
+__global__ void route_bias_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
+                                  int* __restrict__ ids, float* __restrict__ wts, int n_tok, int n_exp, int n_groups,
+                                  int keep, int top, float scale) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const long long t = (long long)blockIdx.x * nw + warp;
+    if (t >= n_tok) return;
+    float* s = sm + (long long)warp * (2 * n_exp + n_groups);
+    float* c = s + n_exp;
+    float* gs = c + n_exp;
+    const int per = n_exp / n_groups;
+    float mx = -INFINITY;
+    for (int e = lane; e < n_exp; e += 32) mx = fmaxf(mx, logits[t * ld + e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < n_exp; e += 32) {
+        const float v = expf(logits[t * ld + e] - mx);
+        s[e] = v;
+        den += v;
+    }
+    den = warp_sum(den);
+    for (int e = lane; e < n_exp; e += 32) {
+        s[e] = s[e] / den;
+        c[e] = s[e] + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (keep < n_groups) {
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY;
+            for (int i = 0; i < per; ++i) a = fmaxf(a, c[g * per + i]);
+            gs[g] = a;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            for (int r = 0; r < keep; ++r) {  // the best `keep` groups are marked with +inf
+                int best = -1;
+                float bv = -INFINITY;
+                for (int g = 0; g < n_groups; ++g)
+                    if (gs[g] != INFINITY && (best < 0 || gs[g] > bv)) {
+                        bv = gs[g];
+                        best = g;
+                    }
+                gs[best] = INFINITY;
+            }
+        }
+        __syncwarp();
+        for (int e = lane; e < n_exp; e += 32)
+            if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    float chosen_w = 0.f;  // lane k keeps choice k (top <= 32)
+    int chosen_e = 0;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int be = 0x7fffffff;
+        for (int e = lane; e < n_exp; e += 32)
+            if (c[e] > bv) {
+                bv = c[e];
+                be = e;
+            }
+        for (int m = 16; m > 0; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, m);
+            if (ov > bv || (ov == bv && oe < be)) {
+                bv = ov;
+                be = oe;
+            }
+        }
+        if (lane == k) {
+            chosen_e = be;
+            chosen_w = s[be];
+        }
+        __syncwarp();
+        if (lane == 0) c[be] = -INFINITY;
+        __syncwarp();
+    }
+    if (lane < top) {
+        ids[t * top + lane] = chosen_e;
+        wts[t * top + lane] = chosen_w * scale;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ sort by expert
-// One block. meta[0] = number of tiles; tiles[i] = (expert, first sorted row, rows).
-__global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, int* __restrict__ perm,
+// One block. meta[0] = number of tiles; tiles[i] = (expert, first sorted row, rows). Experts >= n_real (no weights) keep
+// their place in the sorted order but get no tiles.
+__global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, int n_real, int* __restrict__ perm,
                             int* __restrict__ pos_of, int* __restrict__ tiles, int* __restrict__ meta,
                             int* __restrict__ seg_off, int* __restrict__ tiles256) {
     extern __shared__ int si[];
@@ -133,7 +222,7 @@ __global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, i
     __syncthreads();
     if (threadIdx.x == 32 && tiles256) {  // the GEMM core's tile list (256-row m-blocks), by another warp
         int o = 0, nt = 0;
-        for (int e = 0; e < n_exp; ++e) {
+        for (int e = 0; e < n_real; ++e) {
             for (int r = 0; r < cnt[e]; r += 256) {
                 tiles256[3 * nt] = e;
                 tiles256[3 * nt + 1] = o + r;
@@ -148,7 +237,7 @@ __global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, i
         int o = 0, nt = 0;
         for (int e = 0; e < n_exp; ++e) {
             off[e] = o;
-            for (int r = 0; r < cnt[e]; r += kTileRows) {
+            for (int r = 0; e < n_real && r < cnt[e]; r += kTileRows) {
                 tiles[3 * nt] = e;
                 tiles[3 * nt + 1] = o + r;
                 tiles[3 * nt + 2] = cnt[e] - r < kTileRows ? cnt[e] - r : kTileRows;
@@ -353,14 +442,29 @@ extern "C" int llark_seq_moe_route(const float* logits, long long ld, int* ids, 
     return check_launch();
 }
 
+extern "C" int llark_seq_moe_route_bias(const float* logits, long long ld, const float* correction, int* ids, float* wts,
+                                        int n_tok, int n_exp, int n_groups, int keep, int top, float scale,
+                                        cudaStream_t st) {
+    if (n_tok <= 0 || n_exp <= 0 || n_groups <= 0 || (n_exp % n_groups) || keep <= 0 || keep > n_groups || top <= 0 ||
+        top > 32 || top > keep * (n_exp / n_groups) || !logits || !ids || !wts)
+        return LLARK_EINVAL;
+    const int nw = 4;
+    const size_t smem = sizeof(float) * nw * (size_t)(2 * n_exp + n_groups);
+    if (smem > 48 * 1024) return LLARK_EINVAL;
+    route_bias_kernel<<<(n_tok + nw - 1) / nw, nw * 32, smem, st>>>(logits, ld, correction, ids, wts, n_tok, n_exp,
+                                                                   n_groups, keep, top, scale);
+    return check_launch();
+}
+
 extern "C" int llark_seq_moe_tile_rows(void) { return kTileRows; }
 
-extern "C" int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta,
-                                  int* seg_off, int* tiles256, cudaStream_t st) {
-    if (n_ent <= 0 || n_exp <= 0 || !ids || !perm || !pos_of || !tiles || !meta) return LLARK_EINVAL;
+extern "C" int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int n_real, int* perm, int* pos_of, int* tiles,
+                                  int* meta, int* seg_off, int* tiles256, cudaStream_t st) {
+    if (n_ent <= 0 || n_exp <= 0 || n_real < 0 || n_real > n_exp || !ids || !perm || !pos_of || !tiles || !meta)
+        return LLARK_EINVAL;
     const size_t smem = sizeof(int) * (3 * (size_t)n_exp + 1);
     if (smem > 48 * 1024) return LLARK_EINVAL;
-    sort_kernel<<<1, 1024, smem, st>>>(ids, n_ent, n_exp, perm, pos_of, tiles, meta, seg_off, tiles256);
+    sort_kernel<<<1, 1024, smem, st>>>(ids, n_ent, n_exp, n_real, perm, pos_of, tiles, meta, seg_off, tiles256);
     return check_launch();
 }
 

@@ -505,6 +505,79 @@ __global__ void residual_combine_kernel(const float* __restrict__ x, const float
     }
 }
 
+// ------------------------------------------------------------------------------------------------ norm after the sum
+// x_out = rmsnorm(alpha * x + f) * w for blocks whose norm sits on the residual SUM. f is made of up to two sublayer
+// outputs y1, y2 (each first RMS-normed over the width with its own weight when w1 / w2 is given; with two of them
+// branch_scale weighs their sum) and, optionally, of a mixture's chosen experts: entry k of token t adds wts[t, k] times
+// row pos_of[t * top + k] of z, or times x itself when its expert number ids[t * top + k] >= n_real (an expert that hands
+// its input through). The sum is kept in shared memory between the reduction and the scaling. Block per row.
+template <typename T>
+__global__ void post_norm_kernel(const float* __restrict__ x, float alpha, const float* __restrict__ y1,
+                                 const float* __restrict__ w1, const float* __restrict__ y2, const float* __restrict__ w2,
+                                 float branch_scale, const float* __restrict__ z, const int* __restrict__ pos_of,
+                                 const float* __restrict__ wts, const int* __restrict__ ids, int top, int n_real,
+                                 const float* __restrict__ w, float* __restrict__ x_out, T* __restrict__ x_act, int C,
+                                 float eps) {
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const float* xr = x + t * C;
+    float r1 = 1.f, r2 = 1.f;
+    if (y1 && w1) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) ss = fmaf(y1[t * C + c], y1[t * C + c], ss);
+        r1 = 1.0f / sqrtf(block_sum(ss, red) / (float)C + eps);
+    }
+    if (y2 && w2) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) ss = fmaf(y2[t * C + c], y2[t * C + c], ss);
+        r2 = 1.0f / sqrtf(block_sum(ss, red) / (float)C + eps);
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float xv = xr[c];
+        float f = 0.f;
+        if (y1) f = w1 ? y1[t * C + c] * r1 * w1[c] : y1[t * C + c];
+        if (y2) f += w2 ? y2[t * C + c] * r2 * w2[c] : y2[t * C + c];
+        f *= branch_scale;
+        for (int k = 0; k < top; ++k) {
+            const bool through = ids && ids[t * top + k] >= n_real;
+            f = fmaf(wts[t * top + k], through ? xv : z[(long long)pos_of[t * top + k] * C + c], f);
+        }
+        const float s = fmaf(alpha, xv, f);
+        srow[c] = s;
+        ss = fmaf(s, s, ss);
+    }
+    const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float v = srow[c] * r * w[c];
+        x_out[t * C + c] = v;
+        if (x_act) stf(x_act + t * C + c, v);
+    }
+}
+
+// act = g' * sigmoid(slope * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); gu = [gate | up] rows
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ act, long long rows, int ff, float limit,
+                                   float slope) {
+    const long long n = rows * ff;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / ff;
+        const int c = (int)(i % ff);
+        const float g = fminf(ldf(gu + r * 2 * ff + c), limit);
+        const float u = fminf(fmaxf(ldf(gu + r * 2 * ff + ff + c), -limit), limit);
+        stf(act + i, g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+    }
+}
+
+// logits <- cap * tanh(logits * scale / cap) in place (cap <= 0: only the scale)
+__global__ void logit_cap_kernel(float* __restrict__ z, long long n, float scale, float cap) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = z[i] * scale;
+        z[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+    }
+}
+
 // Few rows, 32-bit weights (router logits while decoding): block per row, the row in shared memory as floats, a warp per
 // output column at a time.
 template <typename TA>
@@ -739,6 +812,44 @@ extern "C" int llark_seq_residual_combine(const float* x, const float* y, const 
     if (n_tok <= 0 || C <= 0 || top < 0 || !x || !y || !x_out || (top > 0 && (!z || !pos_of || !wts)))
         return LLARK_EINVAL;
     residual_combine_kernel<<<n_tok, norm_threads(C * 4), 0, st>>>(x, y, z, pos_of, wts, top, x_out, C);
+    return check_launch();
+}
+
+extern "C" int llark_seq_post_norm(const float* x, float alpha, const float* y1, const float* w1, const float* y2,
+                                   const float* w2, float branch_scale, const float* z, const int* pos_of,
+                                   const float* wts, const int* ids, int top, int n_real, const float* w, float* x_out,
+                                   void* x_act, long long rows, int C, float eps, int act_fp32, cudaStream_t st) {
+    if (rows <= 0 || C <= 0 || top < 0 || !x || !w || !x_out || (top > 0 && (!z || !pos_of || !wts)) || (y2 && !y1) ||
+        (w1 && !y1) || (w2 && !y2))
+        return LLARK_EINVAL;
+    const size_t smem = sizeof(float) * (size_t)C;
+    if (smem > 48 * 1024) return LLARK_EINVAL;
+    const int th = norm_threads(C);
+    if (act_fp32)
+        post_norm_kernel<float><<<(unsigned)rows, th, smem, st>>>(x, alpha, y1, w1, y2, w2, branch_scale, z, pos_of, wts,
+                                                                  ids, top, n_real, w, x_out, (float*)x_act, C, eps);
+    else
+        post_norm_kernel<bf16_t><<<(unsigned)rows, th, smem, st>>>(x, alpha, y1, w1, y2, w2, branch_scale, z, pos_of, wts,
+                                                                   ids, top, n_real, w, x_out, (bf16_t*)x_act, C, eps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_glu_clamped(const void* gu, void* act, long long rows, int ff, float limit, float slope,
+                                     int act_fp32, cudaStream_t st) {
+    if (rows <= 0 || ff <= 0 || !gu || !act || !(limit > 0.f)) return LLARK_EINVAL;
+    const long long n = rows * ff;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (act_fp32)
+        glu_clamped_kernel<float><<<grid, 256, 0, st>>>((const float*)gu, (float*)act, rows, ff, limit, slope);
+    else
+        glu_clamped_kernel<bf16_t><<<grid, 256, 0, st>>>((const bf16_t*)gu, (bf16_t*)act, rows, ff, limit, slope);
+    return check_launch();
+}
+
+extern "C" int llark_seq_logit_cap(float* z, long long n, float scale, float cap, cudaStream_t st) {
+    if (n <= 0 || !z) return LLARK_EINVAL;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    logit_cap_kernel<<<grid, 256, 0, st>>>(z, n, scale, cap);
     return check_launch();
 }
 

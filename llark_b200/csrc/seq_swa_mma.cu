@@ -46,7 +46,7 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
                const bf16_t* __restrict__ kring, const bf16_t* __restrict__ vring, const float* __restrict__ gate,
                long long gate_ld, const float* __restrict__ scale_h, bf16_t* __restrict__ out,
                const int* __restrict__ cu, const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G,
-               int D, int window, int cap) {
+               int D, int window, int cap, const float* __restrict__ sink, int gate_per_head) {
     const int b = blockIdx.z, h = blockIdx.y;
     const int g = h / (H / G);
     const int row0 = cu[b], n = cu[b + 1] - row0;
@@ -238,13 +238,15 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
         const int r = qrow + x * 8;
         if (qt0 + r >= n) continue;
         const long long trow = row0 + qt0 + r;
-        const float inv = 1.0f / l[x];
+        // a sink adds exp(sink_h) to the denominator (m is in units of log2; every row has seen its own key, so m is finite)
+        const float inv = 1.0f / (sink ? l[x] + exp2f(sink[h] * 1.4426950408889634f - m[x]) : l[x]);
+        const float gh = (gate && gate_per_head) ? 1.0f / (1.0f + expf(-gate[trow * gate_ld + h])) : 1.0f;
 #pragma unroll
         for (int nt = 0; nt < DMAX / 8; ++nt) {
             if (nt * 8 < D) {
                 const int c = nt * 8 + 2 * tq;
-                float v0 = o[nt][2 * x] * inv, v1 = o[nt][2 * x + 1] * inv;
-                if (gate) {
+                float v0 = o[nt][2 * x] * inv * gh, v1 = o[nt][2 * x + 1] * inv * gh;
+                if (gate && !gate_per_head) {
                     const float* gp = gate + trow * gate_ld + h * D + c;
                     v0 *= 1.0f / (1.0f + expf(-gp[0]));
                     v1 *= 1.0f / (1.0f + expf(-gp[1]));
@@ -258,7 +260,8 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
 template <int DMAX>
 static int launch(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                   const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu, const int* pos0,
-                  const int* slot, int n_seq, int max_len, int H, int G, int D, int window, int cap, cudaStream_t st) {
+                  const int* slot, int n_seq, int max_len, int H, int G, int D, int window, int cap, const float* sink,
+                  int gate_per_head, cudaStream_t st) {
     const size_t smem = sizeof(bf16_t) * (size_t)(BQ + 4 * BK) * (D + 8);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(swa_mma_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -270,7 +273,7 @@ static int launch(const void* qn, const void* kn, const void* vv, const void* kr
     dim3 grid((max_len + BQ - 1) / BQ, H, n_seq);
     swa_mma_kernel<DMAX><<<grid, 128, smem, st>>>((const bf16_t*)qn, (const bf16_t*)kn, (const bf16_t*)vv,
                                                   (const bf16_t*)kring, (const bf16_t*)vring, gate, gate_ld, scale_h,
-                                                  (bf16_t*)out, cu, pos0, slot, H, G, D, window, cap);
+                                                  (bf16_t*)out, cu, pos0, slot, H, G, D, window, cap, sink, gate_per_head);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         g_last_cuda_error = (int)e;
@@ -287,17 +290,18 @@ using namespace llark;
 extern "C" int llark_seq_swa_attn_mma(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                                       const float* gate, long long gate_ld, const float* scale_h, void* out,
                                       const int* cu, const int* pos0, const int* slot, int n_seq, int max_len, int H,
-                                      int G, int D, int window, int cap, cudaStream_t st) {
+                                      int G, int D, int window, int cap, const float* sink, int gate_per_head,
+                                      cudaStream_t st) {
     if (n_seq <= 0 || max_len <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || (D % 16) || D > 256 || window <= 0 ||
         cap <= 0 || !qn || !kn || !vv || !kring || !vring || !scale_h || !out || !cu || !pos0 || !slot)
         return LLARK_EINVAL;
-    if (gate && (gate_ld % 2)) return LLARK_EINVAL;
+    if (gate && !gate_per_head && (gate_ld % 2)) return LLARK_EINVAL;
     if (D <= 64)
         return swamma::launch<64>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len, H,
-                                  G, D, window, cap, st);
+                                  G, D, window, cap, sink, gate_per_head, st);
     if (D <= 128)
         return swamma::launch<128>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len,
-                                   H, G, D, window, cap, st);
+                                   H, G, D, window, cap, sink, gate_per_head, st);
     return swamma::launch<256>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len, H, G,
-                               D, window, cap, st);
+                               D, window, cap, sink, gate_per_head, st);
 }

@@ -1,4 +1,4 @@
-"""The step function shared by the layer-list decoders of the generation path (Kelutar, Golavik): one `step()` runs a
+"""The step function shared by the layer-list decoders of the generation path (Kelutar, Golavik, Gubulorn): one `step()` runs a
 PACKED batch (llark_b200.state_cache) -- requests that start, go on by a portion of their prompt or decode one token are
 the same kernels with other numbers -- and returns fp32 logits for the rows that are asked for. A model's engine
 subclasses this and says how tokens become the residual stream (`_embed`), what its layers do to it (`_run_layers`) and
@@ -48,6 +48,7 @@ class LayerListEngine:
             for s, n in zip(slots, lens):
                 if cache.length[s] + n > self.max_positions:
                     raise ValueError("a request grows past max_positions")
+        cache.reserve_positions(max(cache.length[s] + n for s, n in zip(slots, lens)))  # per-position stores grow first
         flat = [int(t) for ts in tokens for t in ts]
         if flat and (min(flat) < 0 or max(flat) >= self.cfg.vocab):
             raise ValueError("token id outside the vocabulary")

@@ -17,6 +17,22 @@ the same packed weights and stores of its own.
                                         key channel, unit q / k behind a short convolution + SiLU, gated per-head RMS norm
     "general_delta"     GeneralizedDeltaRule    S <- diag(w) S - (a u)(u^T S) + k v^T, u the unit key; o = S^T r
     "moe"        RoutedExperts          sigmoid router, group-limited top-k, weighted sum of small SwiGLU experts
+    "delta"      ScalarGatedDeltaRule   the gated delta rule with ONE decay per head and a SiLU output gate
+    "sink_attention"  SinkAttention     causal softmax attention over everything before (or a window), grouped key / value
+                                        heads, per-head RMS norm of q and k, no rotation, a query temperature that grows
+                                        with the position, a learned sink term in every softmax denominator, one sigmoid
+                                        gate per head; keys and values live in per-position stores that grow
+    "ssd"        StateSpaceDuality      Mamba-2: S <- exp(-exp(A) dt) S + dt B x^T, y = S^T C + D x behind a short
+                                        convolution of x | B | C, SiLU gate in front of a grouped RMS norm
+    "parallel"   ParallelMixers         a sink_attention ("left") and an ssd ("right") side by side on the same input,
+                                        one fused input projection; the layer takes half the sum of their RMS-normed outputs
+    "clamped_glu"  ClampedGluFF         down(min(g, l) * sigmoid(1.702 min(g, l)) * (clamp(u, -l, l) + 1))
+    "moe_softmax_bias"  BiasedSoftmaxExperts  softmax router whose choice is made on score + a stored correction (groups
+                                        ranked by their best), weights = plain scores, and trailing experts without
+                                        weights that hand their input through
+
+A mixer's `branches(x_act, st, cache)` returns ([(output fp32, norm weight or None), ...], scale): what the layer's residual
+kernel adds up (each output first RMS-normed with its weight when there is one). The default is the one output of forward().
 """
 import math
 
@@ -33,6 +49,19 @@ def _vec(w, name, dev):
 
 def _mat(w, name, dev, act):
     return w[name].to(device=dev, dtype=act).contiguous()
+
+
+def _pad_rows(m, multiple=8):
+    """Zero rows up to a multiple: keeps fused projections of odd total width on the tensor-core path (16-byte rows)."""
+    pad = (-m.shape[0]) % multiple
+    if not pad:
+        return m.contiguous()
+    return torch.cat([m, torch.zeros((pad, m.shape[1]), device=m.device, dtype=m.dtype)]).contiguous()
+
+
+class _OneBranch:
+    def branches(self, x_act, st, cache):
+        return [(self.forward(x_act, st, cache), None)], 1.0
 
 
 class GatedWindowAttentionWeights:
@@ -309,15 +338,233 @@ class GeneralizedDeltaRule:
         return ops.linear(on, w.w_o, out_dtype=F32)
 
 
+class ScalarGatedDeltaRuleWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        H, D = int(spec["heads"]), int(spec["dim"])
+        G, E = int(spec.get("kv_heads", H)), int(spec.get("vdim", D))
+        if H % G:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.D, self.E = H, G, D, E
+        # one projection for q | k | v | beta | decay | gate
+        parts = [_mat(w, pfx + n, dev, act) for n in ("q", "k", "v", "b", "a", "g")]
+        self.n_conv = 2 * G * D + H * E
+        self.b_off, self.a_off, self.g_off = self.n_conv, self.n_conv + H, self.n_conv + 2 * H
+        self.n_in = self.g_off + H * E
+        _expect(pfx, ((torch.cat(parts), (self.n_in, width)),))
+        self.w_in = _pad_rows(torch.cat(parts))
+        self.conv = torch.cat([_vec(w, pfx + "q.conv", dev), _vec(w, pfx + "k.conv", dev), _vec(w, pfx + "v.conv", dev)])
+        self.taps = self.conv.shape[1]
+        if "conv" in spec and int(spec["conv"]) != self.taps:
+            raise ValueError(f"{pfx}: convolution tensors do not fit conv = {spec['conv']}")
+        self.dt_bias, self.rate_log = _vec(w, pfx + "dt_bias", dev), _vec(w, pfx + "A_log", dev)
+        self.norm = _vec(w, pfx + "norm", dev)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        _expect(pfx, ((self.conv, (self.n_conv, self.taps)), (self.dt_bias, (H,)), (self.rate_log, (H,)), (self.norm, (E,)),
+                      (self.w_o, (width, H * E))))
+
+
+class ScalarGatedDeltaRule(_OneBranch):
+    Weights = ScalarGatedDeltaRuleWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        w = weights
+        self.h_state = cache.add_store((w.H, w.D, w.E), F32, zero_on_alloc=True)
+        self.h_carry = cache.add_store((max(w.taps - 1, 1), w.n_conv), F32, zero_on_alloc=True)
+
+    def forward(self, hc, st, cache):
+        return self.mix(ops.linear(hc, self.w.w_in, out_dtype=F32), st, cache)
+
+    def mix(self, pin, st, cache):
+        w = self.w
+        GD = w.G * w.D
+        cv = ops.seq_conv_act(pin[:, :w.n_conv], w.conv, cache.view(self.h_carry), st, silu=True)
+        vec = ops.seq_delta_prep(ops.DELTA_GATED_SCALAR, cv[:, :GD], cv[:, GD:2 * GD], pin[:, w.a_off:w.a_off + w.H],
+                                 pin[:, w.b_off:w.b_off + w.H], w.H, w.G, w.D, dec_bias=w.dt_bias, rate_log=w.rate_log)
+        o = ops.seq_delta_scan(vec, cv[:, 2 * GD:], cache.view(self.h_state), st, w.H, w.D, w.E)
+        on = ops.seq_head_norm_gate(o, w.norm, w.H, w.E, self.eps, self.act, gate=pin[:, w.g_off:w.n_in], gate_silu=True)
+        return ops.linear(on, w.w_o, out_dtype=F32)
+
+
+WINDOW_ALL = 1 << 30  # "window" of an attention that sees every earlier position
+
+
+class SinkAttentionWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        H, D = int(spec["heads"]), int(spec["dim"])
+        G, E = int(spec.get("kv_heads", H)), int(spec.get("vdim", D))
+        if H % G:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.D, self.E = H, G, D, E
+        mask = spec.get("mask") or {}
+        self.window = int(mask["size"]) if mask.get("size") else None  # None: every earlier position
+        temp = spec.get("q_temp") or {}
+        self.temp_coef, self.temp_every = float(temp.get("coef", 0.0)), int(temp.get("every", 0))
+        if self.temp_every < 0:
+            raise ValueError(f"{pfx}: q_temp.every must be positive")
+        # one projection for q | k | v | gate (one gate number per head)
+        parts = [_mat(w, pfx + n, dev, act) for n in ("q", "k", "v", "g")]
+        self.k_off, self.v_off, self.g_off = H * D, (H + G) * D, (H + G) * D + G * E
+        self.n_in = self.g_off + H
+        _expect(pfx, ((torch.cat(parts), (self.n_in, width)),))
+        self.w_in = _pad_rows(torch.cat(parts))
+        self.q_norm, self.k_norm = _vec(w, pfx + "q.norm", dev), _vec(w, pfx + "k.norm", dev)
+        self.sink = _vec(w, pfx + "sink", dev) if pfx + "sink" in w else None
+        self.scale_h = torch.full((H,), float(spec["scale"]), device=dev, dtype=F32)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        _expect(pfx, ((self.q_norm, (D,)), (self.k_norm, (D,)), (self.w_o, (width, H * E))))
+        if self.sink is not None:
+            _expect(pfx, ((self.sink, (H,)),))
+
+
+class SinkAttention(_OneBranch):
+    Weights = SinkAttentionWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        w = weights
+        if w.window is None:  # one entry per position, grown by the cache
+            self.h_k = cache.add_store((w.G * w.D,), act, zero_on_alloc=False, per_position=True)
+            self.h_v = cache.add_store((w.G * w.E,), act, zero_on_alloc=False, per_position=True)
+            self.ring = None
+        else:
+            self.ring = max(1, min(w.window, int(max_positions))) if max_positions else max(1, w.window)
+            self.h_k = cache.add_store((self.ring, w.G * w.D), act, zero_on_alloc=False)
+            self.h_v = cache.add_store((self.ring, w.G * w.E), act, zero_on_alloc=False)
+
+    def forward(self, hc, st, cache):
+        return self.mix(ops.linear(hc, self.w.w_in, out_dtype=F32), st, cache)
+
+    def mix(self, pin, st, cache):
+        w = self.w
+        kring, vring = cache.view(self.h_k), cache.view(self.h_v)
+        cap = self.ring if self.ring is not None else cache.positions
+        single = st.max_len == 1
+        qn, kn, vv = ops.seq_qkv_headnorm(pin, 0, w.k_off, w.v_off, w.q_norm, w.k_norm, w.H, w.G, w.D, w.E, self.eps,
+                                          self.act, st, kring=kring if single else None, vring=vring if single else None,
+                                          cap=cap, temp_coef=w.temp_coef, temp_every=w.temp_every)
+        o = ops.seq_swa_attn(qn, kn, vv, kring, vring, pin[:, w.g_off:w.n_in], pin.stride(0), w.scale_h, st, w.H, w.G, w.D,
+                             w.E, w.window or WINDOW_ALL, cap, from_ring_only=single, sink=w.sink, gate_per_head=True)
+        if not single:
+            ops.seq_kv_ring_write(kn, vv, kring, vring, st, cap)
+        return ops.linear(o, w.w_o, out_dtype=F32)
+
+
+class StateSpaceDualityWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        H, E, N = int(spec["heads"]), int(spec["vdim"]), int(spec["state"])
+        G, NG = int(spec.get("groups", 1)), int(spec.get("norm_groups", 1))
+        if H % G or (H * E) % NG:
+            raise ValueError(f"{pfx}: heads must be a multiple of groups, heads * vdim of norm_groups")
+        self.H, self.E, self.N, self.G, self.NG = H, E, N, G, NG
+        inner = self.inner = H * E
+        self.n_conv = inner + 2 * G * N
+        self.n_in = 2 * inner + 2 * G * N + H  # gate | x | B | C | step size
+        w_in = _mat(w, pfx + "in", dev, act)
+        _expect(pfx, ((w_in, (self.n_in, width)),))
+        self.w_in = _pad_rows(w_in)
+        self.conv, self.conv_b = _vec(w, pfx + "conv", dev), _vec(w, pfx + "conv.b", dev)
+        self.taps = self.conv.shape[1]
+        if "conv" in spec and int(spec["conv"]) != self.taps:
+            raise ValueError(f"{pfx}: convolution tensor does not fit conv = {spec['conv']}")
+        self.dt_bias, self.rate_log, self.skip = (_vec(w, pfx + n, dev) for n in ("dt_bias", "A_log", "D"))
+        self.norm = _vec(w, pfx + "norm", dev)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        _expect(pfx, ((self.conv, (self.n_conv, self.taps)), (self.conv_b, (self.n_conv,)), (self.dt_bias, (H,)),
+                      (self.rate_log, (H,)), (self.skip, (H,)), (self.norm, (inner,)), (self.w_o, (width, inner))))
+
+
+class StateSpaceDuality(_OneBranch):
+    Weights = StateSpaceDualityWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        w = weights
+        self.h_state = cache.add_store((w.H, w.N, w.E), F32, zero_on_alloc=True)
+        self.h_carry = cache.add_store((max(w.taps - 1, 1), w.n_conv), F32, zero_on_alloc=True)
+
+    def forward(self, hc, st, cache):
+        return self.mix(ops.linear(hc, self.w.w_in, out_dtype=F32), st, cache)
+
+    def mix(self, pin, st, cache):
+        w = self.w
+        inner, GN = w.inner, w.G * w.N
+        gate, step = pin[:, :inner], pin[:, inner + w.n_conv:w.n_in]
+        cv = ops.seq_conv_act(pin[:, inner:inner + w.n_conv], w.conv, cache.view(self.h_carry), st, silu=True,
+                              bias=w.conv_b)
+        xs, write, read = cv[:, :inner], cv[:, inner:inner + GN], cv[:, inner + GN:]
+        vec = ops.seq_delta_prep(ops.DELTA_STATE_SPACE, read, write, step, None, w.H, w.G, w.N, dec_bias=w.dt_bias,
+                                 rate_log=w.rate_log)
+        o = ops.seq_delta_scan(vec, xs, cache.view(self.h_state), st, w.H, w.N, w.E, correct=False)
+        y = ops.seq_skip_gate_group_norm(o, xs, w.skip, gate, w.norm, w.H, w.E, w.NG, self.eps, self.act)
+        return ops.linear(y, w.w_o, out_dtype=F32)
+
+
+class ParallelMixersWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        self.left = SinkAttentionWeights(w, pfx + "left.", spec["left"], width, dev, act)
+        self.right = StateSpaceDualityWeights(w, pfx + "right.", spec["right"], width, dev, act)
+        self.left_out, self.right_out = _vec(w, pfx + "left.out", dev), _vec(w, pfx + "right.out", dev)
+        _expect(pfx, ((self.left_out, (width,)), (self.right_out, (width,))))
+        # both read the same input: one projection (each side's rows are already padded to 16-byte multiples)
+        self.n_left = self.left.w_in.shape[0]
+        self.w_in = torch.cat([self.left.w_in, self.right.w_in]).contiguous()
+
+
+class ParallelMixers:
+    Weights = ParallelMixersWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w = weights
+        self.left = SinkAttention(weights.left, cache, eps, act, max_positions)
+        self.right = StateSpaceDuality(weights.right, cache, eps, act, max_positions)
+
+    def branches(self, hc, st, cache):
+        w = self.w
+        pin = ops.linear(hc, w.w_in, out_dtype=F32)
+        yl = self.left.mix(pin[:, :w.n_left], st, cache)
+        yr = self.right.mix(pin[:, w.n_left:], st, cache)
+        return [(yl, w.left_out), (yr, w.right_out)], 0.5
+
+
+class ClampedGluFFWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        F = int(spec["ff"])
+        self.ff, self.limit = F, float(spec["limit"])
+        gate, up = _mat(w, pfx + "gate", dev, act), _mat(w, pfx + "up", dev, act)
+        self.w_down = _mat(w, pfx + "down", dev, act)
+        _expect(pfx, ((gate, (F, width)), (up, (F, width)), (self.w_down, (width, F))))
+        self.w_gu = torch.cat([gate, up]).contiguous()
+
+
+class ClampedGluFF:
+    Weights = ClampedGluFFWeights
+
+    def __init__(self, weights, act):
+        self.w, self.act = weights, act
+
+    def forward(self, x_act):
+        gu = ops.linear(x_act, self.w.w_gu, out_dtype=self.act)
+        return ops.linear(ops.seq_glu_clamped(gu, self.w.limit), self.w.w_down, out_dtype=F32)
+
+    def post_norm(self, x, x_act, alpha, w_norm, eps, act):
+        """rmsnorm(alpha x + ff(x)) * w_norm -> (fp32, copy in act)."""
+        return ops.seq_post_norm(x, alpha, w_norm, eps, y1=self.forward(x_act), act=act)
+
+
 class RoutedExpertsWeights:
+    softmax_bias = False  # True: softmax scores, choice on score + `correction`, plain scores as weights
+
     def __init__(self, w, pfx, spec, width, dev, act):
         r = spec["router"]
         self.n, self.top = int(r["experts"]), int(r["top"])
+        self.n_id = int(r.get("identity", 0))  # trailing router outputs without weights: they hand their input through
+        n_all = self.n_all = self.n + self.n_id
         groups = r.get("groups") or {"count": 1, "keep": 1}
         self.n_groups, self.keep, self.scale = int(groups["count"]), int(groups["keep"]), float(r.get("scale", 1.0))
         ff = int(spec["expert"]["ff"])
         self.ff = ff
-        if self.n % self.n_groups or not 0 < self.keep <= self.n_groups or self.top > self.keep * (self.n // self.n_groups):
+        if n_all % self.n_groups or not 0 < self.keep <= self.n_groups or self.top > self.keep * (n_all // self.n_groups):
             raise ValueError(f"{pfx}: router groups do not fit experts / top")
         self.router = _vec(w, pfx + "router", dev)  # the router runs in fp32 whatever the serving dtype
         # A checkpoint stores bf16, so the router's weights usually ARE bf16 numbers. The product of two bf16 numbers is
@@ -325,13 +572,16 @@ class RoutedExpertsWeights:
         # exact products as the fp32 kernel does, in another order. Rows padded with zeros to a whole 64-wide tile.
         self.router_act = None
         if act == torch.bfloat16 and bool((self.router.to(act).to(F32) == self.router).all()):
-            pad = (-self.n) % 64
+            pad = (-n_all) % 64
             self.router_act = torch.cat([self.router.to(act), torch.zeros((pad, width), device=dev, dtype=act)]).contiguous()
         self.w_gate_up = torch.stack([torch.cat([_mat(w, f"{pfx}e{e}.gate", dev, act), _mat(w, f"{pfx}e{e}.up", dev, act)])
                                       for e in range(self.n)]).contiguous()
         self.w_down = torch.stack([_mat(w, f"{pfx}e{e}.down", dev, act) for e in range(self.n)]).contiguous()
-        _expect(pfx, ((self.router, (self.n, width)), (self.w_gate_up, (self.n, 2 * ff, width)),
+        self.correction = _vec(w, pfx + "correction", dev) if self.softmax_bias else None
+        _expect(pfx, ((self.router, (n_all, width)), (self.w_gate_up, (self.n, 2 * ff, width)),
                       (self.w_down, (self.n, width, ff))))
+        if self.correction is not None:
+            _expect(pfx, ((self.correction, (n_all,)),))
 
 
 class RoutedExperts:
@@ -344,19 +594,40 @@ class RoutedExperts:
     def route(self, x_act):
         w = self.w
         if w.router_act is not None:
-            logits = ops.linear(x_act, w.router_act, out_dtype=F32)[:, :w.n]
+            logits = ops.linear(x_act, w.router_act, out_dtype=F32)[:, :w.n_all]
         else:
             logits = ops.linear_w32(x_act, w.router)
-        return ops.seq_moe_route(logits, w.n_groups, w.keep, w.top, w.scale)
+        return ops.seq_moe_route(logits, w.n_groups, w.keep, w.top, w.scale, softmax_bias=w.softmax_bias,
+                                 correction=w.correction)
 
     def residual(self, x, y, x_act):
         """x + (y + experts(x_act)): fp32 residual sum with the mixer's output y."""
         w = self.w
+        if w.n_id:
+            raise ValueError("experts that hand their input through need the norm-after-sum residual (post_norm)")
         ids, wts = self.route(x_act)
         z, pos_of = ops.seq_moe_experts(x_act, ids, w.w_gate_up, w.w_down)
         return ops.seq_residual_combine(x, y, z, pos_of, wts, w.top)
 
+    def post_norm(self, x, x_act, alpha, w_norm, eps, act):
+        """rmsnorm(alpha x + experts(x)) * w_norm -> (fp32, copy in act); the weighted sum over a token's choices is taken
+        inside the norm kernel, in the order of the choices."""
+        w = self.w
+        ids, wts = self.route(x_act)
+        z, pos_of = ops.seq_moe_experts(x_act, ids, w.w_gate_up, w.w_down, n_through=w.n_id)
+        return ops.seq_post_norm(x, alpha, w_norm, eps, z=z, pos_of=pos_of, wts=wts, ids=ids, n_real=w.n, act=act)
+
+
+class BiasedSoftmaxExpertsWeights(RoutedExpertsWeights):
+    softmax_bias = True
+
+
+class BiasedSoftmaxExperts(RoutedExperts):
+    Weights = BiasedSoftmaxExpertsWeights
+
 
 MIXERS = {"attention": GatedWindowAttention, "hgrn2": GatedLinearRecurrence, "latent_attention": LatentWindowAttention,
-          "channel_delta": GatedDeltaRule, "general_delta": GeneralizedDeltaRule}
-FEED_FORWARDS = {"dense": ReluSquaredFF, "moe": RoutedExperts}
+          "channel_delta": GatedDeltaRule, "general_delta": GeneralizedDeltaRule, "delta": ScalarGatedDeltaRule,
+          "sink_attention": SinkAttention, "ssd": StateSpaceDuality, "parallel": ParallelMixers}
+FEED_FORWARDS = {"dense": ReluSquaredFF, "moe": RoutedExperts, "clamped_glu": ClampedGluFF,
+                 "moe_softmax_bias": BiasedSoftmaxExperts}

@@ -581,21 +581,43 @@ def seq_qk_headnorm(src, q_off, k_off, wq, wk, H, G, D, eps, act, st=None, kring
     return qn, kn, vr
 
 
+def seq_qkv_headnorm(src, q_off, k_off, v_off, wq, wk, H, G, D, E, eps, act, st, kring=None, vring=None, cap=0,
+                     temp_coef=0.0, temp_every=0):
+    """As seq_qk_headnorm with values of their own (E columns per key / value head at v_off, copied un-normed) and an
+    optional temperature on the query that grows with the position: 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)."""
+    _req(src, torch.float32)
+    n = src.shape[0]
+    qn = torch.empty((n, H * D), device=src.device, dtype=act)
+    kn = torch.empty((n, G * D), device=src.device, dtype=act)
+    vv = torch.empty((n, G * E), device=src.device, dtype=act)
+    check(lib().llark_seq_qkv_headnorm(_p(src), src.stride(0), q_off, k_off, v_off, _p(wq), _p(wk), _p(qn), _p(kn), _p(vv),
+                                       _p(kring), _p(vring), _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), n, H, G,
+                                       D, E, cap, float(eps), float(temp_coef), int(temp_every), _actf(act), _stream()),
+          "seq_qkv_headnorm")
+    return qn, kn, vv
+
+
 SWA_MMA_MIN_LEN = 16  # shortest longest-request of a step that goes to the tensor-core attention kernel
 
 
-def seq_swa_attn(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, st, H, G, D, E, window, cap, from_ring_only):
+def seq_swa_attn(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, st, H, G, D, E, window, cap, from_ring_only, sink=None,
+                 gate_per_head=False):
+    """Softmax attention of a packed step over the last `window` positions (rings of `cap` entries per slot hold what
+    earlier steps brought). sink fp32 [H]: one more term exp(sink_h) of the denominator; gate_per_head: gate [n_tok, H]."""
     out = torch.empty((st.n_tok, H * E), device=qn.device, dtype=qn.dtype)
+    if sink is not None:
+        _req(sink, torch.float32)
     if (qn.dtype == BF16 and not from_ring_only and st.max_len >= SWA_MMA_MIN_LEN and D == E and D % 16 == 0
-            and D <= 256 and gate_ld % 2 == 0):
+            and D <= 256 and (gate_per_head or gate_ld % 2 == 0)):
         # prompts and portions: 64-query tiles on the tensor cores; single tokens, fp32 and odd head sizes stay SIMT
         check(lib().llark_seq_swa_attn_mma(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h),
                                            _p(out), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_seq, st.max_len, H, G, D,
-                                           window, cap, _stream()), "seq_swa_attn_mma")
+                                           window, cap, _p(sink), int(gate_per_head), _stream()), "seq_swa_attn_mma")
         return out
     check(lib().llark_seq_swa_attn(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h), _p(out),
                                    _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_tok, H, G, D, E, window, cap,
-                                   int(from_ring_only), _actf(qn.dtype), _stream()), "seq_swa_attn")
+                                   int(from_ring_only), _p(sink), int(gate_per_head), _actf(qn.dtype), _stream()),
+          "seq_swa_attn")
     return out
 
 
@@ -682,23 +704,27 @@ def seq_residual_combine(x, y, z=None, pos_of=None, wts=None, top=0):
     return out
 
 
-def seq_conv_act(src, w, carry, st, silu=True):
+def seq_conv_act(src, w, carry, st, silu=True, bias=None):
     """src fp32 [n_tok, n_ch] (a column slice of a wider matrix is fine), w fp32 [n_ch, taps], carry fp32
-    [slots, taps-1, n_ch] (updated) -> fp32 [n_tok, n_ch] = act(causal depthwise conv)."""
+    [slots, taps-1, n_ch] (updated), bias fp32 [n_ch] or None -> fp32 [n_tok, n_ch] = act(causal depthwise conv)."""
     _req(src, torch.float32), _req(w, torch.float32)
     n_ch, taps = w.shape
     out = torch.empty((st.n_tok, n_ch), device=src.device, dtype=torch.float32)
     check(lib().llark_seq_conv_act(_p(src), src.stride(0), _p(w), _p(carry), _p(st.tok_seq), _p(st.cu), _p(st.slot),
-                                   _p(out), st.n_tok, st.n_seq, n_ch, taps, int(silu), _stream()), "seq_conv_act")
+                                   _p(out), st.n_tok, st.n_seq, n_ch, taps, int(silu), _p(bias), _stream()), "seq_conv_act")
     return out
 
 
-DELTA_GATED, DELTA_GENERALIZED = 0, 1
+DELTA_GATED, DELTA_GENERALIZED, DELTA_GATED_SCALAR, DELTA_STATE_SPACE = 0, 1, 2, 3
 
 
 def seq_delta_prep(rule, q, k, dec, mix, H, G, D, dec_bias=None, rate_log=None, unit_eps=1e-6):
-    """The five vectors [n_tok, H, 5, D] of seq_delta_scan from fp32 projections (column slices are fine)."""
+    """The five vectors [n_tok, H, 5, D] of seq_delta_scan from fp32 projections (column slices are fine).
+    DELTA_GATED_SCALAR: dec [n_tok, H], dec_bias [H] (one decay per head). DELTA_STATE_SPACE: q = the read-out vectors,
+    k = the write vectors [n_tok, G, D], dec = the step size before its softplus [n_tok, H]; mix is not used."""
     n = q.shape[0]
+    if mix is None:
+        mix = dec
     vec = torch.empty((n, H, 5, D), device=q.device, dtype=torch.float32)
     check(lib().llark_seq_delta_prep(int(rule), _p(_req(q, torch.float32)), q.stride(0), _p(_req(k, torch.float32)),
                                      k.stride(0), _p(_req(dec, torch.float32)), dec.stride(0), _p(dec_bias),
@@ -707,24 +733,75 @@ def seq_delta_prep(rule, q, k, dec, mix, H, G, D, dec_bias=None, rate_log=None, 
     return vec
 
 
-def seq_delta_scan(vec, v, state, st, H, D, E):
+def seq_delta_scan(vec, v, state, st, H, D, E, correct=True):
     """vec fp32 [n_tok, H, 5, D], v fp32 [n_tok, H*E] (column slice fine), state fp32 [slots, H, D, E] (updated) ->
-    o fp32 [n_tok, H*E]."""
+    o fp32 [n_tok, H*E]. correct=False: the rule has no correction term (DELTA_STATE_SPACE)."""
     _req(vec, torch.float32), _req(v, torch.float32), _req(state, torch.float32)
     o = torch.empty((st.n_tok, H * E), device=v.device, dtype=torch.float32)
     check(lib().llark_seq_delta_scan(_p(vec), _p(v), v.stride(0), _p(state), _p(o), _p(st.cu), _p(st.slot), st.n_seq,
-                                     st.n_tok, H, D, E, _stream()), "seq_delta_scan")
+                                     st.n_tok, H, D, E, int(correct), _stream()), "seq_delta_scan")
     return o
 
 
-def seq_head_norm_gate(x, w, H, E, eps, act, gate=None, w_per_head=False):
-    """x fp32 [n_tok, H*E]: per-head RMS norm, times w ([E] or [H*E]), times sigmoid(gate fp32 [n_tok, H*E]) -> act."""
+def seq_head_norm_gate(x, w, H, E, eps, act, gate=None, w_per_head=False, gate_silu=False):
+    """x fp32 [n_tok, H*E]: per-head RMS norm, times w ([E] or [H*E]), times sigmoid(gate fp32 [n_tok, H*E]) (gate_silu:
+    times silu(gate)) -> act."""
     _req(x, torch.float32), _req(w, torch.float32)
     out = torch.empty(x.shape, device=x.device, dtype=act)
     check(lib().llark_seq_head_norm_gate(_p(x), _p(w), int(w_per_head), _p(gate), gate.stride(0) if gate is not None else 0,
-                                         _p(out), x.shape[0], H, E, float(eps), _actf(act), _stream()),
+                                         _p(out), x.shape[0], H, E, float(eps), int(gate_silu), _actf(act), _stream()),
           "seq_head_norm_gate")
     return out
+
+
+def seq_skip_gate_group_norm(o, xin, skip, gate, w, H, E, groups, eps, act):
+    """(o + skip[h] * xin) * silu(gate) over the H*E channels of a token, RMS norm in `groups` equal parts, times w -> act.
+    o fp32 [n_tok, H*E] contiguous; xin, gate fp32 column slices."""
+    _req(o, torch.float32), _req(xin, torch.float32), _req(gate, torch.float32), _req(w, torch.float32)
+    out = torch.empty(o.shape, device=o.device, dtype=act)
+    check(lib().llark_seq_skip_gate_group_norm(_p(o), _p(xin), xin.stride(0), _p(_req(skip, torch.float32)), _p(gate),
+                                               gate.stride(0), _p(w), _p(out), o.shape[0], H, E, int(groups), float(eps),
+                                               _actf(act), _stream()), "seq_skip_gate_group_norm")
+    return out
+
+
+def seq_post_norm(x, alpha, w, eps, y1=None, w1=None, y2=None, w2=None, branch_scale=1.0, z=None, pos_of=None, wts=None,
+                  ids=None, n_real=0, act=None):
+    """rmsnorm(alpha * x + f) * w on fp32 rows, f = branch_scale * (b1 + b2) + the chosen experts' weighted outputs:
+    b_i = y_i, or rmsnorm(y_i) * w_i when w_i is given; expert entries (z, pos_of, wts [n_tok, top]) whose number in `ids`
+    is >= n_real add wts * x instead of a row of z. Returns x_out fp32, or (x_out, copy in `act`) when act is given (for
+    act = float32 the copy is x_out itself)."""
+    _req(x, torch.float32), _req(w, torch.float32)
+    rows, C = x.shape
+    out = torch.empty_like(x)
+    xa = torch.empty((rows, C), device=x.device, dtype=act) if act == BF16 else None
+    top = wts.shape[1] if wts is not None else 0
+    check(lib().llark_seq_post_norm(_p(x), float(alpha), _p(y1), _p(w1), _p(y2), _p(w2), float(branch_scale), _p(z),
+                                    _p(pos_of), _p(wts), _p(ids), int(top), int(n_real), _p(w), _p(out), _p(xa), rows, C,
+                                    float(eps), 0, _stream()), "seq_post_norm")
+    if act is None:
+        return out
+    return out, (xa if xa is not None else out)
+
+
+def seq_glu_clamped(gu, limit, slope=1.702):
+    """gu [rows, 2*ff] = [g | u] -> min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+    rows, ff2 = gu.shape
+    if not gu.is_contiguous():
+        raise ValueError("seq_glu_clamped needs contiguous rows")
+    act = torch.empty((rows, ff2 // 2), device=gu.device, dtype=gu.dtype)
+    check(lib().llark_seq_glu_clamped(_p(gu), _p(act), rows, ff2 // 2, float(limit), float(slope), _actf(gu.dtype),
+                                      _stream()), "seq_glu_clamped")
+    return act
+
+
+def seq_logit_cap_(z, scale, cap):
+    """z fp32 <- cap * tanh(z * scale / cap) in place (cap None or <= 0: only the scale)."""
+    _req(z, torch.float32)
+    if not z.is_contiguous():
+        raise ValueError("seq_logit_cap_ needs a contiguous tensor")
+    check(lib().llark_seq_logit_cap(_p(z), z.numel(), float(scale), float(cap or 0.0), _stream()), "seq_logit_cap")
+    return z
 
 
 def seq_latent_prep(q, lat, norm_w, freqs, mult, st, H, Dn, P, R, eps, act, ring=None, cap=0):
@@ -752,10 +829,18 @@ def seq_head_linear(x, x_hs, w, y, y_hs, N, K, gate=None):
     return y
 
 
-def seq_moe_route(logits, n_groups, keep, top, scale):
+def seq_moe_route(logits, n_groups, keep, top, scale, softmax_bias=False, correction=None):
+    """Expert numbers int32 [n, top] and weights fp32 [n, top]. Default: sigmoid scores, groups ranked by the sum of their
+    two best, weights renormalised. softmax_bias: softmax scores, the choice made on score + correction, groups ranked by
+    their best choice score, weights = the plain scores."""
     n, n_exp = logits.shape
     ids = torch.empty((n, top), device=logits.device, dtype=torch.int32)
     wts = torch.empty((n, top), device=logits.device, dtype=torch.float32)
+    if softmax_bias:
+        check(lib().llark_seq_moe_route_bias(_p(_req(logits, torch.float32)), logits.stride(0), _p(correction), _p(ids),
+                                             _p(wts), n, n_exp, int(n_groups), int(keep), int(top), float(scale),
+                                             _stream()), "seq_moe_route_bias")
+        return ids, wts
     check(lib().llark_seq_moe_route(_p(_req(logits, torch.float32)), logits.stride(0), _p(ids), _p(wts), n, n_exp,
                                     int(n_groups), int(keep), int(top), float(scale), _stream()), "seq_moe_route")
     return ids, wts
@@ -766,12 +851,14 @@ def seq_moe_route(logits, n_groups, keep, top, scale):
 MOE_DENSE_MIN_ENTRIES = 2048
 
 
-def seq_moe_experts(x, ids, w_gate_up, w_down):
+def seq_moe_experts(x, ids, w_gate_up, w_down, n_through=0):
     """x act [n_tok, C]; ids int32 [n_tok, top]; w_gate_up act [n_exp, 2*ff, C] (gate rows, then up rows);
-    w_down act [n_exp, C, ff] -> (z fp32 [n_tok*top, C] expert outputs in sorted order, pos_of int32 [n_tok*top])."""
+    w_down act [n_exp, C, ff] -> (z fp32 [n_tok*top, C] expert outputs in sorted order, pos_of int32 [n_tok*top]).
+    n_through: expert numbers n_exp .. n_exp + n_through - 1 have no weights; their rows of z are not written."""
     L = lib()
     n_tok, top = ids.shape
-    n_exp, ff2, C = w_gate_up.shape
+    n_real, ff2, C = w_gate_up.shape
+    n_exp = n_real + int(n_through)
     ff = ff2 // 2
     n_ent = n_tok * top
     dense = (x.dtype == BF16 and n_ent >= MOE_DENSE_MIN_ENTRIES and C % 8 == 0 and ff % 8 == 0 and C >= 64 and ff >= 64
@@ -788,7 +875,7 @@ def seq_moe_experts(x, ids, w_gate_up, w_down):
 
     perm, pos_of, tiles, meta, seg_off, tiles256 = (take(n_ent), take(n_ent), take(3 * max_tiles), take(2),
                                                     take(n_exp + 1), take(3 * max256))
-    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, _p(perm), _p(pos_of), _p(tiles), _p(meta), _p(seg_off),
+    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, n_real, _p(perm), _p(pos_of), _p(tiles), _p(meta), _p(seg_off),
                                _p(tiles256) if dense else None, _stream()), "seq_moe_sort")
     z = torch.empty((n_ent, C), device=x.device, dtype=torch.float32)
     act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
@@ -799,10 +886,10 @@ def seq_moe_experts(x, ids, w_gate_up, w_down):
         xs = torch.empty((n_ent, C), device=x.device, dtype=x.dtype)
         check(L.llark_seq_moe_gather(_p(x), x.stride(0), _p(perm), top, _p(xs), n_ent, C, 0, _stream()), "seq_moe_gather")
         gu = torch.empty((n_ent, ff2), device=x.device, dtype=x.dtype)
-        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, None, n_exp, _p(tiles256), max256, _p(count),
+        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, None, n_real, _p(tiles256), max256, _p(count),
                                     n_ent, ff2, C, _stream()), "gemm_segments(gate|up)")
         check(L.llark_seq_silu_mul(_p(gu), _p(act), n_ent, ff, 0, _stream()), "seq_silu_mul")
-        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, None, n_exp, _p(tiles256), max256, _p(count),
+        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, None, n_real, _p(tiles256), max256, _p(count),
                                     n_ent, C, ff, _stream()), "gemm_segments(down)")
         return z, pos_of
     check(L.llark_seq_moe_up(_p(x), x.stride(0), _p(perm), top, _p(w_gate_up), _p(act), _p(tiles), _p(meta), max_tiles,

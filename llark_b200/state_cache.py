@@ -6,7 +6,10 @@ convolution) and whose requests come and go with different lengths use this inst
 it needs (`add_store`), a request owns one SLOT = one row of every store from `alloc()` to `release()`, and the kernels
 index the stores by slot. Stores of equal shape are stacked into one tensor [n_layers_of_that_kind, n_slots, ...], so
 starting a request zeroes each kind with one fill and a layer's view [n_slots, ...] stays contiguous. Stores grow by
-doubling when the slots run out.
+doubling when the slots run out. A store that holds one entry per POSITION of a request (the keys and values of an
+attention that looks back without a bound) is declared with per_position=True: its first axis is `positions` entries
+long for every such store of the cache and doubles (`reserve_positions`) before a step that would outgrow it, old entries
+kept in place.
 
 Sized for one B200: a ring is min(window, max_positions) entries per slot whatever the sequence length; a recurrent
 state is heads x dim x vdim fp32 per slot.
@@ -83,9 +86,11 @@ StepLayout.chunks = _step_chunks
 
 
 class StateCache:
-    def __init__(self, device, n_slots=4):
+    def __init__(self, device, n_slots=4, positions=256):
         self.device = torch.device(device)
         self.n_slots = int(n_slots)
+        self.positions = max(int(positions), 1)  # entries per slot of the per-position stores
+        self.has_per_position = False
         self._decl = []      # (shape, dtype, zero_on_alloc) per handle
         self._groups = {}    # (shape, dtype, zero) -> [handles]
         self._tensors = {}   # group key -> stacked tensor [count, n_slots, *shape]
@@ -95,12 +100,13 @@ class StateCache:
         self.allocs = 0      # how often a slot was handed out (a reused slot counts again)
 
     # ------------------------------------------------------------------------------------------ stores
-    def add_store(self, shape, dtype, zero_on_alloc):
+    def add_store(self, shape, dtype, zero_on_alloc, per_position=False):
         """Declare a per-slot store of `shape`; returns a handle for view(). All stores must be declared before the
-        first alloc()."""
+        first alloc(). per_position: the store is [positions, *shape] per slot and grows with reserve_positions()."""
         if self._tensors:
             raise RuntimeError("stores must be declared before the cache is used")
-        key = (tuple(int(s) for s in shape), dtype, bool(zero_on_alloc))
+        key = (tuple(int(s) for s in shape), dtype, bool(zero_on_alloc), bool(per_position))
+        self.has_per_position = self.has_per_position or bool(per_position)
         h = len(self._decl)
         self._decl.append(key)
         self._groups.setdefault(key, []).append(h)
@@ -109,8 +115,9 @@ class StateCache:
 
     def _build(self):
         for key, handles in self._groups.items():
-            shape, dtype, _ = key
-            self._tensors[key] = torch.zeros((len(handles), self.n_slots) + shape, device=self.device, dtype=dtype)
+            shape, dtype, _, per_pos = key
+            lead = (self.positions,) if per_pos else ()
+            self._tensors[key] = torch.zeros((len(handles), self.n_slots) + lead + shape, device=self.device, dtype=dtype)
 
     def view(self, handle):
         """The store as [n_slots, *shape] (contiguous). Fetch it every step: growing the cache replaces the tensors."""
@@ -122,8 +129,8 @@ class StateCache:
     def bytes_per_slot(self):
         n = 0
         for key, handles in self._groups.items():
-            shape, dtype, _ = key
-            e = 1
+            shape, dtype, _, per_pos = key
+            e = self.positions if per_pos else 1
             for s in shape:
                 e *= s
             n += e * len(handles) * torch.empty((), dtype=dtype).element_size()
@@ -138,6 +145,21 @@ class StateCache:
             bigger[:, :old].copy_(t)
             self._tensors[key] = bigger
         self._free.extend(range(self.n_slots - 1, old - 1, -1))
+
+    def reserve_positions(self, n):
+        """Make room for requests of up to n tokens in the per-position stores (doubling; entries keep their place)."""
+        if n <= self.positions or not self.has_per_position:
+            return
+        new = self.positions
+        while new < n:
+            new *= 2
+        if self._tensors:
+            for key, t in list(self._tensors.items()):
+                if key[3]:
+                    bigger = torch.zeros(t.shape[:2] + (new,) + t.shape[3:], device=self.device, dtype=t.dtype)
+                    bigger[:, :, :self.positions].copy_(t)
+                    self._tensors[key] = bigger
+        self.positions = new
 
     def alloc(self):
         """A slot for a new request: its recurrent / convolution state starts at zero, it holds no tokens."""
