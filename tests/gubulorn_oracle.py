@@ -217,6 +217,84 @@ def forward(cfg, W, tokens, return_residuals=False):
             x = norm_one_plus(alpha * x + f, W[p + "norm2"], eps)
         residuals.append(x)
     z = (norm_one_plus(x, W["final.norm"], eps) @ W["head"].T) * cfg["logit_scale"]
-    cap = cfg["logit_softcap"]
-    z = cap * torch.tanh(z / cap)
+    cap = cfg.get("logit_softcap")
+    if cap is not None:
+        z = cap * torch.tanh(z / cap)
     return (z, residuals) if return_residuals else z
+
+
+# ------------------------------------------------------------------------------------------------ random checkpoints
+def random_weights(cfg, seed=0, dtype=torch.float64):
+    """Random weights of a configuration, rounded to bfloat16 (what a checkpoint stores) and returned in `dtype`. Router
+    corrections are large enough to make choice scores negative; sinks, skips and decays are of order one."""
+    g = torch.Generator().manual_seed(seed)
+    C, V = cfg["width"], cfg["vocab"]
+    W = {}
+
+    def mat(name, out, inp, scale=1.0):
+        W[name] = torch.randn(out, inp, generator=g) * scale / math.sqrt(inp)
+
+    def vec(name, n, mean=0.0, std=1.0):
+        W[name] = mean + std * torch.randn(n, generator=g)
+
+    W["embed"] = torch.randn(V, C, generator=g)
+    mat("head", V, C, 2.0)
+    vec("embed.norm", C, 0.0, 0.1)
+    vec("final.norm", C, 0.0, 0.1)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        vec(p + "norm1", C, 0.0, 0.1)
+        x = p + "mix."
+        if L["type"] == "delta":
+            H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * E)):
+                mat(x + n, rows, C, 2.0)
+                W[x + n + ".conv"] = torch.randn(rows, m["conv"], generator=g) * 0.5
+            mat(x + "b", H, C)
+            mat(x + "a", H, C)
+            W[x + "A_log"] = torch.rand(H, generator=g) * 2.0 - 2.0
+            vec(x + "dt_bias", H, -1.0, 1.0)
+            vec(x + "norm", E, 1.0, 0.1)
+            mat(x + "g", H * E, C)
+            mat(x + "o", C, H * E)
+        else:
+            a, b = m["left"], m["right"]
+            H, G, D, E = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            mat(x + "left.q", H * D, C, 2.0)
+            mat(x + "left.k", G * D, C, 2.0)
+            mat(x + "left.v", G * E, C)
+            vec(x + "left.q.norm", D, 1.0, 0.2)
+            vec(x + "left.k.norm", D, 1.0, 0.2)
+            vec(x + "left.sink", H, 0.5, 1.0)
+            mat(x + "left.g", H, C, 2.0)
+            mat(x + "left.o", C, H * E)
+            vec(x + "left.out", C, 1.0, 0.1)
+            Hs, Es, N, Gs = b["heads"], b["vdim"], b["state"], b["groups"]
+            inner, nc = Hs * Es, Hs * Es + 2 * Gs * N
+            mat(x + "right.in", 2 * inner + 2 * Gs * N + Hs, C, 1.5)
+            W[x + "right.conv"] = torch.randn(nc, b["conv"], generator=g) * 0.5
+            vec(x + "right.conv.b", nc, 0.0, 0.3)
+            vec(x + "right.dt_bias", Hs, -1.0, 1.0)
+            W[x + "right.A_log"] = torch.rand(Hs, generator=g) * 2.0 - 2.0
+            vec(x + "right.D", Hs, 1.0, 0.5)
+            vec(x + "right.norm", inner, 1.0, 0.1)
+            mat(x + "right.o", C, inner)
+            vec(x + "right.out", C, 1.0, 0.1)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        vec(p + "norm2", C, 0.0, 0.1)
+        if mlp["kind"] == "dense":
+            mat(p + "mlp.gate", mlp["ff"], C, 2.0)
+            mat(p + "mlp.up", mlp["ff"], C, 2.0)
+            mat(p + "mlp.down", C, mlp["ff"])
+        else:
+            r = mlp["router"]
+            n_all = r["experts"] + r.get("identity", 0)
+            mat(p + "mlp.router", n_all, C, 2.0)
+            vec(p + "mlp.correction", n_all, -0.05, 0.15)
+            for e in range(r["experts"]):
+                mat(f"{p}mlp.e{e}.gate", mlp["expert"]["ff"], C)
+                mat(f"{p}mlp.e{e}.up", mlp["expert"]["ff"], C)
+                mat(f"{p}mlp.e{e}.down", C, mlp["expert"]["ff"])
+    return {k: v.to(torch.bfloat16).to(dtype) for k, v in W.items()}
