@@ -181,7 +181,8 @@ def _op_work(name, a, k, out, ctx):
         return _nbytes(src) + 2 * st.n_seq * H * D * E * 4 + st.n_tok * H * E * 4, 5.0 * st.n_tok * H * D * E
     if name == "seq_delta_scan":
         vec, v, state, st, H, D, E = a[0], a[1], a[2], a[3], a[4], a[5], a[6]
-        return (_nbytes(vec) + st.n_tok * H * E * 8 + 2 * st.n_seq * H * D * E * 4), 9.0 * st.n_tok * H * D * E
+        per = 9.0 if k.get("correct", True) else 5.0  # without the correction: decay, write and read-out only
+        return (_nbytes(vec) + st.n_tok * H * E * 8 + 2 * st.n_seq * H * D * E * 4), per * st.n_tok * H * D * E
     if name == "seq_moe_experts":
         x, ids, wgu, wd = a[0], a[1], a[2], a[3]
         n_ent, (n_exp, ff2, C) = ids.numel(), wgu.shape
@@ -388,6 +389,128 @@ def run_golavik(args, peaks, peaks_kind, emit):
           "warmup": max(args.warmup, 3), "ms_per_step": head["prefill"]["golavik_ms"], "higher_is_better": True,
           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
           "config": {"model": "Golavik " + head["size"], "l2": "256 MB fill between timed steps",
+                     "peaks": peaks_kind, "hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]},
+          "sizes": results, "wall_s": round(time.time() - t0, 1)})
+
+
+GUBULORN_OPS = ["linear", "linear_w32", "seq_embed", "seq_post_norm", "seq_rmsnorm_rows", "seq_conv_act", "seq_delta_prep",
+                "seq_delta_scan", "seq_head_norm_gate", "seq_skip_gate_group_norm", "seq_qkv_headnorm", "seq_swa_attn",
+                "seq_kv_ring_write", "seq_moe_route", "seq_moe_experts", "seq_glu_clamped", "seq_logit_cap_"]
+
+# (name, width, layers, heads, head dim, experts, pass-through experts, top, expert ff, state-space heads, state size,
+# vocab): layers repeat delta, parallel, parallel, delta, each with a routed feed-forward except the first (a clamped gated
+# unit of top x expert-ff rows); the state-space side has heads of 64 channels. The Golavik model beside it has the same
+# width, layer count, heads, head size, experts, top and expert ff, and a window as long as the prompt.
+GUBULORN_SIZES = [
+    ("u2048", 2048, 4, 16, 128, 32, 8, 4, 1024, 64, 128, 32000),
+    ("u4096", 4096, 4, 32, 128, 64, 8, 6, 1024, 128, 128, 32000),
+]
+
+
+def gubulorn_config(width, layers, heads, dim, experts, through, top, ff, ss_heads, state, vocab):
+    moe = {"kind": "moe", "expert": {"ff": ff},
+           "router": {"experts": experts, "identity": through, "top": top, "groups": {"count": 8, "keep": 4}}}
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4}}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": dim, "vdim": dim,
+                              "scale": 1.0 / math.sqrt(dim), "q_temp": {"coef": 0.1, "every": 512}},
+                     "right": {"heads": ss_heads, "vdim": 64, "state": state, "groups": 8, "norm_groups": 8, "conv": 4}}}
+    kinds = [delta, par, par, delta]
+    ls = [dict(kinds[i % 4], mlp=moe) for i in range(layers)]
+    ls[0]["mlp"] = {"kind": "dense", "ff": top * ff, "limit": 7.0}
+    return {"architecture": "Gubulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "logit_scale": 1.0, "logit_softcap": 30.0, "layers": ls}
+
+
+def gubulorn_random_weights(cfg, device, seed=0):
+    g = torch.Generator(device=device).manual_seed(seed)
+    C = cfg["width"]
+
+    def mat(o, i, s=None):
+        return (torch.randn(o, i, device=device, generator=g) * (s or 1.0 / math.sqrt(i))).to(BF16)
+
+    def vec(n, mean=1.0, s=0.1):
+        return (mean + torch.randn(n, device=device, generator=g) * s).to(BF16)
+
+    W = {"embed": mat(cfg["vocab"], C, 1.0), "embed.norm": vec(C, 0.0), "final.norm": vec(C, 0.0),
+         "head": mat(cfg["vocab"], C)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, layer["mixer"]
+        x = p + "mix."
+        W[p + "norm1"], W[p + "norm2"] = vec(C, 0.0), vec(C, 0.0)
+        if layer["type"] == "delta":
+            H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * E)):
+                W[x + n], W[x + n + ".conv"] = mat(rows, C), mat(rows, m["conv"], 0.5)
+            W.update({x + "b": mat(H, C), x + "a": mat(H, C), x + "A_log": vec(H, -1.0, 0.5), x + "dt_bias": vec(H, -1.0, 1.0),
+                      x + "norm": vec(E), x + "g": mat(H * E, C), x + "o": mat(C, H * E)})
+        else:
+            a, b = m["left"], m["right"]
+            H, G, D, E = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            W.update({x + "left.q": mat(H * D, C), x + "left.k": mat(G * D, C), x + "left.v": mat(G * E, C),
+                      x + "left.q.norm": vec(D), x + "left.k.norm": vec(D), x + "left.sink": vec(H, 0.0, 1.0),
+                      x + "left.g": mat(H, C), x + "left.o": mat(C, H * E), x + "left.out": vec(C)})
+            Hs, Es, N, Gs = b["heads"], b["vdim"], b["state"], b["groups"]
+            inner, nc = Hs * Es, Hs * Es + 2 * Gs * N
+            W.update({x + "right.in": mat(2 * inner + 2 * Gs * N + Hs, C), x + "right.conv": mat(nc, b["conv"], 0.5),
+                      x + "right.conv.b": vec(nc, 0.0, 0.3), x + "right.dt_bias": vec(Hs, -1.0, 1.0),
+                      x + "right.A_log": vec(Hs, -1.0, 0.5), x + "right.D": vec(Hs), x + "right.norm": vec(inner),
+                      x + "right.o": mat(C, inner), x + "right.out": vec(C)})
+        mlp = layer["mlp"]
+        if mlp["kind"] == "dense":
+            W.update({p + "mlp.gate": mat(mlp["ff"], C), p + "mlp.up": mat(mlp["ff"], C), p + "mlp.down": mat(C, mlp["ff"])})
+        else:
+            r, f = mlp["router"], mlp["expert"]["ff"]
+            W[p + "mlp.router"] = mat(r["experts"] + r["identity"], C)
+            W[p + "mlp.correction"] = vec(r["experts"] + r["identity"], 0.0, 0.01)
+            for e in range(r["experts"]):
+                W.update({"%smlp.e%d.gate" % (p, e): mat(f, C), "%smlp.e%d.up" % (p, e): mat(f, C),
+                          "%smlp.e%d.down" % (p, e): mat(C, f)})
+    return W
+
+
+def bench_size_gubulorn(name, width, layers, heads, dim, experts, through, top, ff, ss_heads, state, vocab, peaks, steps,
+                        warmup, prefill_batch=4, prompt=2048, decode_batches=(1, 8, 32), context=1024):
+    """Gubulorn beside Golavik (the closest existing decoder: delta-rule scans, attention over a per-slot store and routed
+    experts on the same step function, cache and linears) at equal width, layer count, heads, experts and expert size."""
+    from llark_b200.models.golavik import GolavikConfig, GolavikForCausalLM
+    from llark_b200.models.gubulorn import GubulornConfig, GubulornForCausalLM
+
+    flush = _Flush()
+    out = {"size": name, "width": width, "layers": layers, "heads": heads, "head_dim": dim, "experts": experts,
+           "pass_through_experts": through, "top": top, "expert_ff": ff, "state_space_heads": ss_heads, "state": state,
+           "vocab": vocab, "prefill": {"batch": prefill_batch, "prompt": prompt}, "decode": {"context": context}}
+    g = torch.Generator().manual_seed(0)
+    cfg = gubulorn_config(width, layers, heads, dim, experts, through, top, ff, ss_heads, state, vocab)
+    um = GubulornForCausalLM(GubulornConfig.from_dict(cfg), gubulorn_random_weights(cfg, "cuda"), dtype=BF16)
+    um.engine.max_positions = max(prompt, context) + 64
+    bench_native("gubulorn", um.engine, GUBULORN_OPS, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt,
+                 decode_batches, context)
+    del um
+    torch.cuda.empty_cache()
+    gcfg = golavik_config(width, layers, heads, dim, max(prompt, context), experts, top, ff, 192, 64, vocab)
+    gm = GolavikForCausalLM(GolavikConfig.from_dict(gcfg), golavik_random_weights(gcfg, "cuda"), dtype=BF16)
+    bench_native("golavik", gm.engine, GOLAVIK_OPS, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt,
+                 decode_batches, context)
+    del gm
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_gubulorn(args, peaks, peaks_kind, emit):
+    from llark_b200 import ops
+
+    ops.init()
+    t0 = time.time()
+    sizes = [s for s in GUBULORN_SIZES if not os.environ.get("LLARK_BENCH_SIZE") or s[0] == os.environ["LLARK_BENCH_SIZE"]]
+    results = [bench_size_gubulorn(*s, peaks=peaks, steps=args.steps, warmup=max(args.warmup, 3)) for s in sizes]
+    head = results[0]
+    emit({"metric": "generation tokens/s, Gubulorn beside Golavik at equal size (prefill of %d x %d tokens)"
+                    % (head["prefill"]["batch"], head["prefill"]["prompt"]),
+          "value": head["prefill"]["gubulorn_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 3), "ms_per_step": head["prefill"]["gubulorn_ms"], "higher_is_better": True,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
+          "config": {"model": "Gubulorn " + head["size"], "l2": "256 MB fill between timed steps",
                      "peaks": peaks_kind, "hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]},
           "sizes": results, "wall_s": round(time.time() - t0, 1)})
 

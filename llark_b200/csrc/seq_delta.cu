@@ -430,6 +430,54 @@ __global__ void skip_gate_group_norm_kernel(const float* __restrict__ o, const f
     }
 }
 
+// The same with the part's values kept in shared memory between the two passes (one read of every input) and 16-byte
+// accesses: per, E, x_ld and gate_ld multiples of 4, every pointer 16-byte aligned.
+template <typename T>
+__global__ void skip_gate_group_norm4_kernel(const float* __restrict__ o, const float* __restrict__ xin, long long x_ld,
+                                             const float* __restrict__ skip, const float* __restrict__ gate,
+                                             long long gate_ld, const float* __restrict__ w, T* __restrict__ out, int H,
+                                             int E, int groups, float eps) {
+    extern __shared__ float4 sy4[];
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const int inner = H * E, per = inner / groups, c0 = blockIdx.y * per, per4 = per >> 2;
+    const float4* o4 = reinterpret_cast<const float4*>(o + t * inner + c0);
+    const float4* x4 = reinterpret_cast<const float4*>(xin + t * x_ld + c0);
+    const float4* g4 = reinterpret_cast<const float4*>(gate + t * gate_ld + c0);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < per4; i += blockDim.x) {
+        const float4 ov = o4[i], xv = x4[i], gv = g4[i];
+        const float sk = skip[(c0 + 4 * i) / E];
+        float4 y;
+        y.x = fmaf(sk, xv.x, ov.x) * (gv.x * sigmoidf_(gv.x));
+        y.y = fmaf(sk, xv.y, ov.y) * (gv.y * sigmoidf_(gv.y));
+        y.z = fmaf(sk, xv.z, ov.z) * (gv.z * sigmoidf_(gv.z));
+        y.w = fmaf(sk, xv.w, ov.w) * (gv.w * sigmoidf_(gv.w));
+        sy4[i] = y;
+        ss = fmaf(y.x, y.x, fmaf(y.y, y.y, fmaf(y.z, y.z, fmaf(y.w, y.w, ss))));
+    }
+    ss = warp_sum(ss);
+    const int wi = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) red[wi] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)per + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w + c0);
+    for (int i = threadIdx.x; i < per4; i += blockDim.x) {
+        const float4 y = sy4[i], ww = w4[i];
+        T* dst = out + t * inner + c0 + 4 * i;
+        if constexpr (sizeof(T) == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(y.x * r * ww.x, y.y * r * ww.y, y.z * r * ww.z, y.w * r * ww.w);
+        } else {
+            uint2 u;
+            u.x = pack_bf16x2(y.x * r * ww.x, y.y * r * ww.y);
+            u.y = pack_bf16x2(y.z * r * ww.z, y.w * r * ww.w);
+            *reinterpret_cast<uint2*>(dst) = u;
+        }
+    }
+}
+
 }  // namespace delta
 }  // namespace llark
 
@@ -569,6 +617,20 @@ extern "C" int llark_seq_skip_gate_group_norm(const float* o, const float* xin, 
     int th = 32;
     while (th < per && th < 256) th <<= 1;
     dim3 grid((unsigned)n_tok, groups);
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (per % 4 == 0 && E % 4 == 0 && x_ld % 4 == 0 && gate_ld % 4 == 0 && al(o) && al(xin) && al(gate) && al(w) && al(out) &&
+        (size_t)per * sizeof(float) <= 48 * 1024) {
+        int t4 = 32;
+        while (t4 * 8 < per && t4 < 256) t4 <<= 1;
+        const size_t smem = sizeof(float) * (size_t)per;
+        if (act_fp32)
+            skip_gate_group_norm4_kernel<float><<<grid, t4, smem, st>>>(o, xin, x_ld, skip, gate, gate_ld, w, (float*)out, H,
+                                                                        E, groups, eps);
+        else
+            skip_gate_group_norm4_kernel<__nv_bfloat16><<<grid, t4, smem, st>>>(o, xin, x_ld, skip, gate, gate_ld, w,
+                                                                                (__nv_bfloat16*)out, H, E, groups, eps);
+        return check_launch();
+    }
     if (act_fp32)
         skip_gate_group_norm_kernel<float><<<grid, th, 0, st>>>(o, xin, x_ld, skip, gate, gate_ld, w, (float*)out, H, E,
                                                                 groups, eps);

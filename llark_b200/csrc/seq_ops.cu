@@ -556,6 +556,86 @@ __global__ void post_norm_kernel(const float* __restrict__ x, float alpha, const
     }
 }
 
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    uint2 u;
+    u.x = pack_bf16x2(v.x, v.y);
+    u.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// The same with 16-byte accesses (C a multiple of 4, every pointer 16-byte aligned).
+template <typename T>
+__global__ void post_norm4_kernel(const float* __restrict__ x, float alpha, const float* __restrict__ y1,
+                                  const float* __restrict__ w1, const float* __restrict__ y2, const float* __restrict__ w2,
+                                  float branch_scale, const float* __restrict__ z, const int* __restrict__ pos_of,
+                                  const float* __restrict__ wts, const int* __restrict__ ids, int top, int n_real,
+                                  const float* __restrict__ w, float* __restrict__ x_out, T* __restrict__ x_act, int C,
+                                  float eps) {
+    extern __shared__ float4 srow4[];
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const int C4 = C >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + t * C);
+    const float4* a1 = y1 ? reinterpret_cast<const float4*>(y1 + t * C) : nullptr;
+    const float4* a2 = y2 ? reinterpret_cast<const float4*>(y2 + t * C) : nullptr;
+    float r1 = 1.f, r2 = 1.f;
+    if (a1 && w1) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < C4; c += blockDim.x) {
+            const float4 v = a1[c];
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        r1 = 1.0f / sqrtf(block_sum(ss, red) / (float)C + eps);
+    }
+    if (a2 && w2) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < C4; c += blockDim.x) {
+            const float4 v = a2[c];
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        r2 = 1.0f / sqrtf(block_sum(ss, red) / (float)C + eps);
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C4; c += blockDim.x) {
+        const float4 xv = xr[c];
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a1) {
+            f = a1[c];
+            if (w1) {
+                const float4 ww = reinterpret_cast<const float4*>(w1)[c];
+                f = make_float4(f.x * r1 * ww.x, f.y * r1 * ww.y, f.z * r1 * ww.z, f.w * r1 * ww.w);
+            }
+        }
+        if (a2) {
+            float4 g = a2[c];
+            if (w2) {
+                const float4 ww = reinterpret_cast<const float4*>(w2)[c];
+                g = make_float4(g.x * r2 * ww.x, g.y * r2 * ww.y, g.z * r2 * ww.z, g.w * r2 * ww.w);
+            }
+            f = make_float4(f.x + g.x, f.y + g.y, f.z + g.z, f.w + g.w);
+        }
+        f = make_float4(f.x * branch_scale, f.y * branch_scale, f.z * branch_scale, f.w * branch_scale);
+        for (int k = 0; k < top; ++k) {
+            const bool through = ids && ids[t * top + k] >= n_real;
+            const float wt = wts[t * top + k];
+            const float4 e = through ? xv : reinterpret_cast<const float4*>(z + (long long)pos_of[t * top + k] * C)[c];
+            f = make_float4(fmaf(wt, e.x, f.x), fmaf(wt, e.y, f.y), fmaf(wt, e.z, f.z), fmaf(wt, e.w, f.w));
+        }
+        const float4 sv = make_float4(fmaf(alpha, xv.x, f.x), fmaf(alpha, xv.y, f.y), fmaf(alpha, xv.z, f.z),
+                                      fmaf(alpha, xv.w, f.w));
+        srow4[c] = sv;
+        ss = fmaf(sv.x, sv.x, fmaf(sv.y, sv.y, fmaf(sv.z, sv.z, fmaf(sv.w, sv.w, ss))));
+    }
+    const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)C + eps);
+    for (int c = threadIdx.x; c < C4; c += blockDim.x) {
+        const float4 sv = srow4[c], ww = reinterpret_cast<const float4*>(w)[c];
+        const float4 v = make_float4(sv.x * r * ww.x, sv.y * r * ww.y, sv.z * r * ww.z, sv.w * r * ww.w);
+        st4(x_out + t * C + 4 * c, v);
+        if (x_act) st4(x_act + t * C + 4 * c, v);
+    }
+}
+
 // act = g' * sigmoid(slope * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); gu = [gate | up] rows
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ act, long long rows, int ff, float limit,
@@ -824,6 +904,20 @@ extern "C" int llark_seq_post_norm(const float* x, float alpha, const float* y1,
         return LLARK_EINVAL;
     const size_t smem = sizeof(float) * (size_t)C;
     if (smem > 48 * 1024) return LLARK_EINVAL;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (C % 4 == 0 && al(x) && al(y1) && al(w1) && al(y2) && al(w2) && al(z) && al(w) && al(x_out) && al(x_act)) {
+        int t4 = 32;
+        while (t4 * 8 < C && t4 < 256) t4 <<= 1;  // two vectors per thread at the usual widths
+        if (act_fp32)
+            post_norm4_kernel<float><<<(unsigned)rows, t4, smem, st>>>(x, alpha, y1, w1, y2, w2, branch_scale, z, pos_of,
+                                                                       wts, ids, top, n_real, w, x_out, (float*)x_act, C,
+                                                                       eps);
+        else
+            post_norm4_kernel<bf16_t><<<(unsigned)rows, t4, smem, st>>>(x, alpha, y1, w1, y2, w2, branch_scale, z, pos_of,
+                                                                        wts, ids, top, n_real, w, x_out, (bf16_t*)x_act,
+                                                                        C, eps);
+        return check_launch();
+    }
     const int th = norm_threads(C);
     if (act_fp32)
         post_norm_kernel<float><<<(unsigned)rows, th, smem, st>>>(x, alpha, y1, w1, y2, w2, branch_scale, z, pos_of, wts,
