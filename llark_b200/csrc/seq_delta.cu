@@ -49,7 +49,7 @@ __global__ void conv_act_kernel(const float* __restrict__ src, long long ld, con
     const int b = tok_seq[t];
     const int local = t - cu[b];
     float* cr = carry + (long long)slot[b] * (taps - 1) * n_ch;
-    for (int c = threadIdx.x; c < n_ch; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n_ch; c += gridDim.y * blockDim.x) {
         const float cur = src[(long long)t * ld + c];
         float acc = bias ? bias[c] : 0.f;
         for (int j = 0; j < taps - 1; ++j) {
@@ -506,8 +506,11 @@ extern "C" int llark_seq_conv_act(const float* src, long long ld, const float* w
             conv_act_rows_kernel<4, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu,
                                                               bias);
     } else {
-        conv_act_kernel<<<n_tok, th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu, inline_carry,
-                                              bias);
+        // few rows (decode): the channels are spread over blocks too, so that a handful of tokens still fills the GPU
+        int gy = (n_ch + th - 1) / th;
+        if ((long long)gy * n_tok > 4 * 148) gy = (4 * 148 + n_tok - 1) / n_tok;
+        conv_act_kernel<<<dim3(n_tok, gy), th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu,
+                                                        inline_carry, bias);
     }
     int rc = check_launch();
     if (rc != LLARK_OK || inline_carry || taps == 1) return rc;
