@@ -1,4 +1,5 @@
-"""Generation throughput of the Kelutar path beside the Llama path at equal size (`bench.py --workload generation`).
+"""Generation throughput of the Kelutar path beside the Llama path at equal size (`bench.py --workload generation`), of
+Golavik beside Kelutar (`generation-golavik`) and of Gubulorn beside Golavik (`generation-gubulorn`).
 
 Random weights, synthetic token ids. For each size: prefill tokens/s (a packed batch of whole prompts) and decode tokens/s
 (one token per request and step, after a prompt of `context` tokens) for both decoders, plus a per-op table: every op
