@@ -289,6 +289,11 @@ int llark_seq_conv_tail(const float* h, float* tail, const int* cu, const int* s
  * caller); x_act (optional) receives x_out in the activation dtype. */
 int llark_seq_add_rmsnorm(const float* x, const float* y, const float* w, float* x_out, void* x_act, long long rows, int C,
                           float eps, int act_fp32, cudaStream_t stream);
+/* x_out = x + rmsnorm(y * sigmoid(gate)) * w (gate optional: a column slice with row pitch gate_ld); when x_act != NULL it
+ * also receives rmsnorm(x_out) * w_next in the activation dtype (the next sublayer's input norm). All norms over the row. */
+int llark_seq_gated_norm_add(const float* x, const float* y, const float* gate, long long gate_ld, const float* w,
+                             const float* w_next, float* x_out, void* x_act, long long rows, int C, float eps,
+                             int act_fp32, cudaStream_t stream);
 /* out[i] = rmsnorm(x[rows[i]]) * w in the activation dtype (rows == NULL: row i). */
 int llark_seq_rmsnorm_rows(const float* x, const int* rows, const float* w, void* out, int n_rows, int C, float eps,
                            int act_fp32, cudaStream_t stream);
@@ -313,24 +318,39 @@ int llark_seq_qkv_headnorm(const float* src, long long ld, int q_off, int k_off,
                            const float* wk, void* qn, void* kn, void* vv, void* kring, void* vring, const int* tok_seq,
                            const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int cap,
                            float eps, float temp_coef, int temp_every, int act_fp32, cudaStream_t stream);
+/* q / k / v of a fused projection with rotary positions. wq / wk (both or neither): RMS norm over the WHOLE q (H*D) and k
+ * (G*D) projection with weights of that size. qk_freq fp32 [n_rot / 2]: the first n_rot entries of every q / k head are
+ * rotated by position * qk_freq[i], pairs (i, i + n_rot/2) or, qk_interleaved, (2i, 2i + 1). v_freq fp32 [E / 2] (optional):
+ * every value head is rotated the same way over all of E. Results in the activation dtype; with kring / vring the k / v rows
+ * also go to ring entry position % cap of the slot. */
+int llark_seq_qkv_rotary(const float* src, long long ld, int q_off, int k_off, int v_off, const float* wq, const float* wk,
+                         const float* qk_freq, int n_rot, int qk_interleaved, const float* v_freq, int v_interleaved,
+                         void* qn, void* kn, void* vv, void* kring, void* vring, const int* tok_seq, const int* cu,
+                         const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int cap, float eps,
+                         int act_fp32, cudaStream_t stream);
 /* Sliding-window softmax attention: query at position i sees keys j with 0 <= i - j < window. Keys / values of this
  * step come from kn / vv ([n_tok, G, D] / [n_tok, G, E]), earlier ones from the rings [slots, cap, G, D|E] (entry
  * j % cap); from_ring_only = 1: the step's own token is already in the ring. score = q.k * scale_h[h]; the output is
  * multiplied by sigmoid(gate[t, h*E + e]) when gate != NULL (gate_per_head: by sigmoid(gate[t, h])). sink (optional)
  * fp32 [H]: exp(sink[h]), unscaled, is one more term of head h's softmax denominator; it has no value. A window of at
- * least cap positions with cap >= the longest sequence is plain causal attention. out [n_tok, H, E]. */
+ * least cap positions with cap >= the longest sequence is plain causal attention. chunk > 0 replaces the window: the query
+ * sees j <= i with floor(j / chunk) = floor(i / chunk). softcap > 0: score <- softcap * tanh(score / softcap). vfreq fp32
+ * [E / 2] (optional): the values are stored rotated by their own position (llark_seq_qkv_rotary); each head's weighted sum is
+ * turned back by the query's position before the gate (v_interleaved: pairs (2m, 2m + 1), else (m, m + E/2)).
+ * out [n_tok, H, E]. */
 int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                        const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
                        const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
-                       int cap, int from_ring_only, const float* sink, int gate_per_head, int act_fp32,
-                       cudaStream_t stream);
+                       int cap, int from_ring_only, const float* sink, int gate_per_head, int chunk, float softcap,
+                       const float* vfreq, int v_interleaved, int act_fp32, cudaStream_t stream);
 /* The same attention for steps that bring many tokens per request (prompts, portions): bf16 only, D = E a multiple of
  * 16 up to 256, 64-query CTAs on mma.sync with fp32 scores / softmax (csrc/seq_swa_mma.cu). max_len = the longest
- * request of the step. */
+ * request of the step. Un-rotation in halves needs D = 64, 128 or 256. */
 int llark_seq_swa_attn_mma(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                            const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu,
                            const int* pos0, const int* slot, int n_seq, int max_len, int H, int G, int D, int window,
-                           int cap, const float* sink, int gate_per_head, cudaStream_t stream);
+                           int cap, const float* sink, int gate_per_head, int chunk, float softcap, const float* vfreq,
+                           int v_interleaved, cudaStream_t stream);
 int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq, const int* cu,
                             const int* pos0, const int* slot, int n_tok, int GD, int GE, int cap, int act_fp32,
                             cudaStream_t stream);
@@ -403,11 +423,12 @@ int llark_seq_glu_clamped(const void* gu, void* act, long long rows, int ff, flo
 /* z <- cap * tanh(z * scale / cap) in place (cap <= 0: z * scale) */
 int llark_seq_logit_cap(float* z, long long n, float scale, float cap, cudaStream_t stream);
 /* latent attention: normed latent and rotated shared key part -> ckr ACT [n_tok, R + P] (and the ring row of the
- * token's position when ring != NULL), rotated query parts -> qf ACT [n_tok, H, R + P] columns R.. */
+ * token's position when ring != NULL), rotated query parts -> qf ACT [n_tok, H, R + P] columns R.. Rotary pairs are
+ * (2i, 2i + 1), or with halves = 1 (i, i + n_rot / 2). */
 int llark_seq_latent_prep(const float* q, long long q_ld, const float* lat, long long lat_ld, const float* norm_w,
                           const float* freqs, int n_rot, float mult, void* ckr, void* qf, void* ring, const int* tok_seq,
                           const int* cu, const int* pos0, const int* slot, int n_tok, int H, int Dn, int P, int R, int cap,
-                          float eps, int act_fp32, cudaStream_t stream);
+                          float eps, int halves, int act_fp32, cudaStream_t stream);
 /* y[m, h * y_hs + n] = sum_k x[m, h * x_hs + k] * w[h][n][k] (* sigmoid(gate[m, h * N + n])) */
 int llark_seq_head_linear(const void* x, int x_fp32, long long ldx, int x_hs, const void* w, void* y, long long ldy,
                           int y_hs, const float* gate, long long gate_ld, int M, int H, int N, int K, int act_fp32,

@@ -26,7 +26,7 @@ SEQ_SYMBOLS = [
     "llark_seq_head_linear", "llark_seq_moe_route", "llark_seq_moe_tile_rows", "llark_seq_moe_sort", "llark_seq_moe_up",
     "llark_seq_moe_down", "llark_seq_tanh", "llark_seq_moe_gather", "llark_seq_silu_mul",
     "llark_seq_qkv_headnorm", "llark_seq_skip_gate_group_norm", "llark_seq_post_norm", "llark_seq_glu_clamped",
-    "llark_seq_logit_cap", "llark_seq_moe_route_bias",
+    "llark_seq_logit_cap", "llark_seq_moe_route_bias", "llark_seq_qkv_rotary", "llark_seq_gated_norm_add",
 ]
 # what libllark_serve.so (`make serve`: GEMM core + decode linears + the ops above) exports
 SERVE_SYMBOLS = SEQ_SYMBOLS + ["llark_last_cuda_error", "llark_init", "llark_gemm", "llark_gemm_ex", "llark_gemv",
@@ -152,8 +152,11 @@ def lib():
             "llark_linear_simt": ([P, LL, P, LL, P, LL, I, P, I, I, I, I, P], I),
             "llark_seq_qk_headnorm": ([P, LL, I, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P], I),
             "llark_seq_qkv_headnorm": ([P, LL, I, I, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, I, P], I),
-            "llark_seq_swa_attn": ([P, P, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, I, P], I),
-            "llark_seq_swa_attn_mma": ([P, P, P, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, I, I, P, I, P], I),
+            "llark_seq_swa_attn": ([P, P, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, I, F, P, I, I, P], I),
+            "llark_seq_swa_attn_mma": ([P, P, P, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, I, I, P, I, I, F, P, I, P], I),
+            "llark_seq_qkv_rotary": ([P, LL, I, I, I, P, P, P, I, I, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I,
+                                      P], I),
+            "llark_seq_gated_norm_add": ([P, P, P, LL, P, P, P, P, LL, I, F, I, P], I),
             "llark_seq_kv_ring_write": ([P, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
             "llark_seq_glr_scan": ([P, LL, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I, I, P], I),
             "llark_seq_glr_combine": ([P, P, P, P, P, I, I, I, I, P], I),
@@ -170,7 +173,7 @@ def lib():
             "llark_seq_glu_clamped": ([P, P, LL, I, F, F, I, P], I),
             "llark_seq_logit_cap": ([P, LL, F, F, P], I),
             "llark_seq_moe_route_bias": ([P, LL, P, P, P, I, I, I, I, I, F, P], I),
-            "llark_seq_latent_prep": ([P, LL, P, LL, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P], I),
+            "llark_seq_latent_prep": ([P, LL, P, LL, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P], I),
             "llark_seq_head_linear": ([P, I, LL, I, P, P, LL, I, P, LL, I, I, I, I, I, P], I),
             "llark_seq_moe_route": ([P, LL, P, P, I, I, I, I, I, F, P], I),
             "llark_seq_moe_tile_rows": ([], I),

@@ -7,7 +7,7 @@
 // so attention runs as H query heads of size R + P over ONE shared key head whose rows are also the values (the last P
 // output channels are not used), through the window-attention kernels of seq_mixers.cu / seq_swa_mma.cu.
 //
-//   llark_seq_latent_prep   RMS norm of the latent, rotation (interleaved pairs, given frequency table and magnitude
+//   llark_seq_latent_prep   RMS norm of the latent, rotation (interleaved pairs or halves, given frequency table and magnitude
 //                           factor) of the shared key part and of every head's rotated query part at the token's
 //                           position (fp32 angles); writes [c | rot k] (also straight into the ring on single-token
 //                           steps) and the rotated query parts into the folded-query buffer
@@ -43,7 +43,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, long long q_ld, 
                                    int n_rot, float mult, T* __restrict__ ckr, T* __restrict__ qf, T* __restrict__ ring,
                                    const int* __restrict__ tok_seq, const int* __restrict__ cu,
                                    const int* __restrict__ pos0, const int* __restrict__ slot, int H, int Dn, int P, int R,
-                                   int cap, float eps) {
+                                   int cap, float eps, int halves) {
     __shared__ float red[32];
     __shared__ float cs[2 * 128];  // cos / sin of up to 128 pairs; more are recomputed
     const int t = blockIdx.x;
@@ -75,7 +75,9 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, long long q_ld, 
         stf(row + c, v);
         if (rrow) stf(rrow + c, v);
     }
-    auto turn = [&](const float* in, int i, float& a, float& bb) {  // pair i of a rotated part
+    // pair i of a rotated part: entries (2i, 2i + 1), or (i, i + half) in the halves layout
+    const int pu = halves ? 1 : 2, pv0 = halves ? half : 1;
+    auto turn = [&](const float* in, int i, float& a, float& bb) {
         float co, si;
         if (i < 128) {
             co = cs[2 * i];
@@ -85,7 +87,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, long long q_ld, 
             co = cosf(ang) * mult;
             si = sinf(ang) * mult;
         }
-        const float u = in[2 * i], v = in[2 * i + 1];
+        const float u = in[pu * i], v = in[pu * i + pv0];
         a = u * co - v * si;
         bb = v * co + u * si;
     };
@@ -93,11 +95,11 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, long long q_ld, 
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float a, bb;
         turn(lr + R, i, a, bb);
-        stf(row + R + 2 * i, a);
-        stf(row + R + 2 * i + 1, bb);
+        stf(row + R + pu * i, a);
+        stf(row + R + pu * i + pv0, bb);
         if (rrow) {
-            stf(rrow + R + 2 * i, a);
-            stf(rrow + R + 2 * i + 1, bb);
+            stf(rrow + R + pu * i, a);
+            stf(rrow + R + pu * i + pv0, bb);
         }
     }
     for (int c = 2 * half + threadIdx.x; c < P; c += blockDim.x) {  // entries past the rotated ones pass
@@ -110,8 +112,8 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, long long q_ld, 
         float a, bb;
         turn(q + (long long)t * q_ld + (long long)h * (Dn + P) + Dn, j, a, bb);
         T* o = qf + ((long long)t * H + h) * W + R;
-        stf(o + 2 * j, a);
-        stf(o + 2 * j + 1, bb);
+        stf(o + pu * j, a);
+        stf(o + pu * j + pv0, bb);
     }
     const int rest = P - 2 * half;
     for (int i = threadIdx.x; i < H * rest; i += blockDim.x) {
@@ -179,7 +181,7 @@ typedef __nv_bfloat16 bf16_t;
 extern "C" int llark_seq_latent_prep(const float* q, long long q_ld, const float* lat, long long lat_ld,
                                      const float* norm_w, const float* freqs, int n_rot, float mult, void* ckr, void* qf,
                                      void* ring, const int* tok_seq, const int* cu, const int* pos0, const int* slot,
-                                     int n_tok, int H, int Dn, int P, int R, int cap, float eps, int act_fp32,
+                                     int n_tok, int H, int Dn, int P, int R, int cap, float eps, int halves, int act_fp32,
                                      cudaStream_t st) {
     if (n_tok <= 0 || H <= 0 || Dn < 0 || P < 0 || R <= 0 || n_rot < 0 || (n_rot % 2) || n_rot > P || !q || !lat ||
         !norm_w || (n_rot && !freqs) || !ckr || !qf || !tok_seq || !cu || !pos0 || !slot || (ring && cap <= 0))
@@ -187,11 +189,11 @@ extern "C" int llark_seq_latent_prep(const float* q, long long q_ld, const float
     if (act_fp32)
         latent_prep_kernel<float><<<n_tok, 128, 0, st>>>(q, q_ld, lat, lat_ld, norm_w, freqs, n_rot, mult, (float*)ckr,
                                                          (float*)qf, (float*)ring, tok_seq, cu, pos0, slot, H, Dn, P, R,
-                                                         cap, eps);
+                                                         cap, eps, halves);
     else
         latent_prep_kernel<bf16_t><<<n_tok, 128, 0, st>>>(q, q_ld, lat, lat_ld, norm_w, freqs, n_rot, mult, (bf16_t*)ckr,
                                                           (bf16_t*)qf, (bf16_t*)ring, tok_seq, cu, pos0, slot, H, Dn, P, R,
-                                                          cap, eps);
+                                                          cap, eps, halves);
     return check_launch();
 }
 

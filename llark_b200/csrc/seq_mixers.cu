@@ -4,7 +4,11 @@
 //
 //   llark_seq_qk_headnorm   per-head RMS norm of the q and k columns of a fused projection; the raw k is kept as well
 //                           (designs whose values are the un-normed keys); optionally writes the ring directly (decode)
-//   llark_seq_swa_attn      softmax attention over a sliding window: keys of this step from the step's buffers, older
+//   llark_seq_qkv_rotary    optional whole-projection RMS norm of q and k, rotary positions on q / k (halves or interleaved
+//                           pairs, partial head) and optionally on the values; optionally writes the rings (decode)
+//   llark_seq_swa_attn      softmax attention over a sliding window (or the query's block of `chunk` positions; scores
+//                           optionally squashed by cap * tanh(s / cap); weighted value sums optionally turned back by the
+//                           query's position): keys of this step from the step's buffers, older
 //                           ones from the per-slot ring of the last `cap` positions; per-head score scale; optional
 //                           sigmoid output gate; scores, softmax and accumulation in fp32
 //   llark_seq_kv_ring_write stores the step's keys / values into the ring (after attention has read the old entries)
@@ -91,6 +95,125 @@ __global__ void qk_headnorm_kernel(const float* __restrict__ src, long long ld, 
     }
 }
 
+// ------------------------------------------------------------------------------------------------ q / k / v with rotary positions
+// src [n_tok, ld] fp32 with q heads (H x D) at q_off, k heads (G x D) at k_off, v heads (G x E) at v_off. Block per token.
+//   wq / wk (optional): RMS norm over the WHOLE q (H*D numbers) and the whole k (G*D) projection, weights of that size
+//   qk_freq [n_rot / 2] (optional): the first n_rot entries of every q and k head are rotated by position * qk_freq[i];
+//            pair i = (i, i + n_rot/2) ("halves") or (2i, 2i+1) (qk_interleaved); the rest of the head passes
+//   v_freq [E / 2] (optional): every value head is rotated by its position the same way over all of E (v_interleaved);
+//            the attention kernels turn their weighted sums back by the query's position
+// Angles are float(position) * frequency, cos / sin in fp32. Results in T; with kring / vring the k / v rows also go to
+// ring entry position % cap of the token's slot (steps of one token per request).
+template <typename T>
+__global__ void qkv_rotary_kernel(const float* __restrict__ src, long long ld, int q_off, int k_off, int v_off,
+                                  const float* __restrict__ wq, const float* __restrict__ wk,
+                                  const float* __restrict__ qk_freq, int n_rot, int qk_interleaved,
+                                  const float* __restrict__ v_freq, int v_interleaved, T* __restrict__ qn,
+                                  T* __restrict__ kn, T* __restrict__ vv, T* __restrict__ kring, T* __restrict__ vring,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                  const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D, int E,
+                                  int cap, float eps) {
+    extern __shared__ float cs[];  // cos | sin of the q / k pairs [2 * (n_rot / 2)], then of the value pairs [2 * (E / 2)]
+    __shared__ float red[2][32];
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const long long p = pos0[b] + (t - cu[b]);
+    const int hq = n_rot >> 1, hv = v_freq ? (E >> 1) : 0;
+    float* csv = cs + 2 * hq;
+    for (int i = threadIdx.x; i < hq; i += blockDim.x) sincosf((float)p * qk_freq[i], &cs[2 * i + 1], &cs[2 * i]);
+    for (int i = threadIdx.x; i < hv; i += blockDim.x) sincosf((float)p * v_freq[i], &csv[2 * i + 1], &csv[2 * i]);
+    const float* row = src + (long long)t * ld;
+    float rq = 1.f, rk = 1.f;
+    if (wq) {  // wk comes with it
+        float sq = 0.f, sk = 0.f;
+        for (int c = threadIdx.x; c < H * D; c += blockDim.x) sq = fmaf(row[q_off + c], row[q_off + c], sq);
+        for (int c = threadIdx.x; c < G * D; c += blockDim.x) sk = fmaf(row[k_off + c], row[k_off + c], sk);
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+        if (l == 0) {
+            red[0][w] = sq;
+            red[1][w] = sk;
+        }
+        __syncthreads();
+        sq = sk = 0.f;
+        for (int i = 0; i < nw; ++i) {
+            sq += red[0][i];
+            sk += red[1][i];
+        }
+        rq = 1.0f / sqrtf(sq / (float)(H * D) + eps);
+        rk = 1.0f / sqrtf(sk / (float)(G * D) + eps);
+    } else {
+        __syncthreads();
+    }
+    T *rk_row = nullptr, *rv_row = nullptr;
+    if (kring) {
+        const long long e = (long long)slot[b] * cap + (p % cap);
+        rk_row = kring + e * G * D;
+        rv_row = vring + e * G * E;
+    }
+    // q and k heads: hh < H is a query head, the others key heads
+    const int per_head = hq + (D - 2 * hq);  // work items of a head: its pairs, then the entries that pass
+    for (int i = threadIdx.x; i < (H + G) * per_head; i += blockDim.x) {
+        const int hh = i / per_head, j = i % per_head;
+        const bool is_q = hh < H;
+        const int head = is_q ? hh : hh - H;
+        const int c0 = head * D;
+        const float* s = row + (is_q ? q_off : k_off) + c0;
+        const float* w = is_q ? wq : wk;
+        const float r = is_q ? rq : rk;
+        T* o = is_q ? qn + (long long)t * H * D + c0 : kn + (long long)t * G * D + c0;
+        T* o2 = (!is_q && rk_row) ? rk_row + c0 : nullptr;
+        if (j < hq) {
+            const int iu = qk_interleaved ? 2 * j : j, iv = qk_interleaved ? 2 * j + 1 : j + hq;
+            float u = s[iu] * r, v = s[iv] * r;
+            if (w) {
+                u *= w[c0 + iu];
+                v *= w[c0 + iv];
+            }
+            const float co = cs[2 * j], si = cs[2 * j + 1];
+            const float a = u * co - v * si, bb = v * co + u * si;
+            stf(o + iu, a);
+            stf(o + iv, bb);
+            if (o2) {
+                stf(o2 + iu, a);
+                stf(o2 + iv, bb);
+            }
+        } else {
+            const int c = 2 * hq + (j - hq);
+            float u = s[c] * r;
+            if (w) u *= w[c0 + c];
+            stf(o + c, u);
+            if (o2) stf(o2 + c, u);
+        }
+    }
+    // value heads
+    const int per_v = v_freq ? hv + (E - 2 * hv) : E;
+    for (int i = threadIdx.x; i < G * per_v; i += blockDim.x) {
+        const int head = i / per_v, j = i % per_v;
+        const int c0 = head * E;
+        const float* s = row + v_off + c0;
+        T* o = vv + (long long)t * G * E + c0;
+        T* o2 = rv_row ? rv_row + c0 : nullptr;
+        if (j < hv) {
+            const int iu = v_interleaved ? 2 * j : j, iv = v_interleaved ? 2 * j + 1 : j + hv;
+            const float u = s[iu], v = s[iv];
+            const float co = csv[2 * j], si = csv[2 * j + 1];
+            const float a = u * co - v * si, bb = v * co + u * si;
+            stf(o + iu, a);
+            stf(o + iv, bb);
+            if (o2) {
+                stf(o2 + iu, a);
+                stf(o2 + iv, bb);
+            }
+        } else {
+            const int c = v_freq ? 2 * hv + (j - hv) : j;
+            stf(o + c, s[c]);
+            if (o2) stf(o2 + c, s[c]);
+        }
+    }
+}
+
 // N consecutive elements -> float, with one 4 / 8 / 16-byte load per piece when `vec` (the address is then aligned to
 // the piece); scalar loads otherwise.
 template <typename T, int N>
@@ -136,7 +259,8 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
                                 const int* __restrict__ tok_seq, const int* __restrict__ cu,
                                 const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D, int E,
                                 int window, int cap, int from_ring_only, const float* __restrict__ sink,
-                                int gate_per_head) {
+                                int gate_per_head, int chunk, float softcap, const float* __restrict__ vfreq,
+                                int v_interleaved) {
     extern __shared__ float sm[];
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* sq = sm;                      // [D]
@@ -149,7 +273,9 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
     const int b = tok_seq[t];
     const long long p0 = pos0[b];
     const long long p = p0 + (t - cu[b]);
-    const long long lo = p - window + 1 > 0 ? p - window + 1 : 0;
+    // first visible key: the start of the query's block of `chunk` positions (blocks counted from position 0), or the
+    // start of the sliding window
+    const long long lo = chunk > 0 ? (p / chunk) * chunk : (p - window + 1 > 0 ? p - window + 1 : 0);
     const int nkeys = (int)(p - lo + 1);
     const float sc = scale_h[h];
     for (int d = threadIdx.x; d < D; d += blockDim.x) sq[d] = ldf(qn + ((long long)t * H + h) * D + d);
@@ -185,6 +311,7 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
                 for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldf(kr + d), dot);
             }
             s = dot * sc;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float mt = warp_max(s);
         const float mn = fmaxf(m, mt);
@@ -233,13 +360,45 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
     for (int w = 0; w < nw; ++w) mm = fmaxf(mm, sm_m[w]);
     float lt = sink ? expf(sink[h] - mm) : 0.f;
     for (int w = 0; w < nw; ++w) lt += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * expf(sm_m[w] - mm);
+    if (!vfreq) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            float o = 0.f;
+            for (int w = 0; w < nw; ++w)
+                if (sm_m[w] != -INFINITY) o = fmaf(sacc[w * E + e], expf(sm_m[w] - mm), o);
+            o /= lt;
+            if (gate) o *= sigmoidf_(gate[(long long)t * gate_ld + (gate_per_head ? h : h * E + e)]);
+            stf(out + ((long long)t * H + h) * E + e, o);
+        }
+        return;
+    }
+    // Values were stored rotated by their own position: the weighted sum is turned back by the query's position, pair m
+    // by -p * vfreq[m], before the gate. The normalised row passes through shared memory (E more floats behind sacc).
+    float* so = sacc + nw * E;
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < nw; ++w)
             if (sm_m[w] != -INFINITY) o = fmaf(sacc[w * E + e], expf(sm_m[w] - mm), o);
-        o /= lt;
-        if (gate) o *= sigmoidf_(gate[(long long)t * gate_ld + (gate_per_head ? h : h * E + e)]);
-        stf(out + ((long long)t * H + h) * E + e, o);
+        so[e] = o / lt;
+    }
+    __syncthreads();
+    const int half = E >> 1;
+    for (int mpair = threadIdx.x; mpair < half; mpair += blockDim.x) {
+        const int iu = v_interleaved ? 2 * mpair : mpair, iv = v_interleaved ? 2 * mpair + 1 : mpair + half;
+        float si, co;
+        sincosf((float)p * vfreq[mpair], &si, &co);
+        const float u = so[iu], v = so[iv];
+        float a = u * co + v * si, bb = v * co - u * si;  // rotation by the negative angle
+        if (gate) {
+            a *= sigmoidf_(gate[(long long)t * gate_ld + (gate_per_head ? h : h * E + iu)]);
+            bb *= sigmoidf_(gate[(long long)t * gate_ld + (gate_per_head ? h : h * E + iv)]);
+        }
+        stf(out + ((long long)t * H + h) * E + iu, a);
+        stf(out + ((long long)t * H + h) * E + iv, bb);
+    }
+    if ((E & 1) && threadIdx.x == 0) {  // an odd last channel has no partner and passes
+        float o = so[E - 1];
+        if (gate) o *= sigmoidf_(gate[(long long)t * gate_ld + (gate_per_head ? h : h * E + E - 1)]);
+        stf(out + ((long long)t * H + h) * E + E - 1, o);
     }
 }
 
@@ -489,21 +648,49 @@ extern "C" int llark_seq_qkv_headnorm(const float* src, long long ld, int q_off,
                            H, G, D, E, cap, eps, temp_coef, temp_every, act_fp32, st);
 }
 
+extern "C" int llark_seq_qkv_rotary(const float* src, long long ld, int q_off, int k_off, int v_off, const float* wq,
+                                    const float* wk, const float* qk_freq, int n_rot, int qk_interleaved,
+                                    const float* v_freq, int v_interleaved, void* qn, void* kn, void* vv, void* kring,
+                                    void* vring, const int* tok_seq, const int* cu, const int* pos0, const int* slot,
+                                    int n_tok, int H, int G, int D, int E, int cap, float eps, int act_fp32,
+                                    cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || G <= 0 || D <= 0 || E <= 0 || !src || !qn || !kn || !vv || !tok_seq || !cu || !pos0 ||
+        !slot || n_rot < 0 || (n_rot % 2) || n_rot > D || (n_rot && !qk_freq) || (!wq != !wk))
+        return LLARK_EINVAL;
+    if (kring && (!vring || cap <= 0)) return LLARK_EINVAL;
+    const size_t smem = sizeof(float) * (size_t)(n_rot + (v_freq ? 2 * (E / 2) : 0));
+    if (smem > 48 * 1024) return LLARK_EINVAL;
+    const int threads = 128;
+    if (act_fp32)
+        qkv_rotary_kernel<float><<<n_tok, threads, smem, st>>>(src, ld, q_off, k_off, v_off, wq, wk, qk_freq, n_rot,
+                                                               qk_interleaved, v_freq, v_interleaved, (float*)qn, (float*)kn,
+                                                               (float*)vv, (float*)kring, (float*)vring, tok_seq, cu, pos0,
+                                                               slot, H, G, D, E, cap, eps);
+    else
+        qkv_rotary_kernel<bf16_t><<<n_tok, threads, smem, st>>>(src, ld, q_off, k_off, v_off, wq, wk, qk_freq, n_rot,
+                                                                qk_interleaved, v_freq, v_interleaved, (bf16_t*)qn,
+                                                                (bf16_t*)kn, (bf16_t*)vv, (bf16_t*)kring, (bf16_t*)vring,
+                                                                tok_seq, cu, pos0, slot, H, G, D, E, cap, eps);
+    return check_launch();
+}
+
 template <typename T>
 static int launch_swa(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                       const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
                       const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
-                      int cap, int from_ring_only, const float* sink, int gate_per_head, cudaStream_t st) {
+                      int cap, int from_ring_only, const float* sink, int gate_per_head, int chunk, float softcap,
+                      const float* vfreq, int v_interleaved, cudaStream_t st) {
+    const int span = chunk > 0 ? chunk : window;  // most keys a query sees
     int nw = 1;
-    while (nw < 8 && nw * 64 < window) nw <<= 1;  // two tiles per warp before another warp pays off
-    const size_t smem = sizeof(float) * (size_t)(D + nw * 32 + 2 * nw + nw * E);
+    while (nw < 8 && nw * 64 < span) nw <<= 1;  // two tiles per warp before another warp pays off
+    const size_t smem = sizeof(float) * (size_t)(D + nw * 32 + 2 * nw + nw * E + (vfreq ? E : 0));
     dim3 grid(n_tok, H);
     const int dpl = (E + 31) / 32;
 #define LLARK_SWA(DPL)                                                                                              \
     swa_attn_kernel<T, DPL><<<grid, nw * 32, smem, st>>>((const T*)qn, (const T*)kn, (const T*)vv, (const T*)kring, \
                                                          (const T*)vring, gate, gate_ld, scale_h, (T*)out, tok_seq, \
                                                          cu, pos0, slot, H, G, D, E, window, cap, from_ring_only, \
-                                                         sink, gate_per_head)
+                                                         sink, gate_per_head, chunk, softcap, vfreq, v_interleaved)
     if (dpl <= 1) LLARK_SWA(1);
     else if (dpl <= 2) LLARK_SWA(2);
     else if (dpl <= 4) LLARK_SWA(4);
@@ -519,16 +706,19 @@ extern "C" int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv
                                   const float* gate, long long gate_ld, const float* scale_h, void* out,
                                   const int* tok_seq, const int* cu, const int* pos0, const int* slot, int n_tok, int H,
                                   int G, int D, int E, int window, int cap, int from_ring_only, const float* sink,
-                                  int gate_per_head, int act_fp32, cudaStream_t st) {
+                                  int gate_per_head, int chunk, float softcap, const float* vfreq, int v_interleaved,
+                                  int act_fp32, cudaStream_t st) {
     if (n_tok <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || E <= 0 || window <= 0 || cap <= 0 || !qn || !kring ||
-        !vring || !scale_h || !out || !tok_seq || !cu || !pos0 || !slot)
+        !vring || !scale_h || !out || !tok_seq || !cu || !pos0 || !slot || chunk < 0 || softcap < 0.f)
         return LLARK_EINVAL;
     if (!from_ring_only && (!kn || !vv)) return LLARK_EINVAL;
-    if ((size_t)(D + 8 * 32 + 16 + 8 * E) * sizeof(float) > 48 * 1024) return LLARK_EINVAL;
+    if ((size_t)(D + 8 * 32 + 16 + 9 * E) * sizeof(float) > 48 * 1024) return LLARK_EINVAL;
     return act_fp32 ? launch_swa<float>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, tok_seq, cu, pos0, slot,
-                                        n_tok, H, G, D, E, window, cap, from_ring_only, sink, gate_per_head, st)
+                                        n_tok, H, G, D, E, window, cap, from_ring_only, sink, gate_per_head, chunk,
+                                        softcap, vfreq, v_interleaved, st)
                     : launch_swa<bf16_t>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, tok_seq, cu, pos0, slot,
-                                         n_tok, H, G, D, E, window, cap, from_ring_only, sink, gate_per_head, st);
+                                         n_tok, H, G, D, E, window, cap, from_ring_only, sink, gate_per_head, chunk,
+                                         softcap, vfreq, v_interleaved, st);
 }
 
 extern "C" int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq,

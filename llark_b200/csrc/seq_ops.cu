@@ -12,6 +12,7 @@
 //   llark_seq_short_conv    y = h + causal depthwise conv(h) with carry-in of the last taps-1 inputs per request
 //   llark_seq_conv_tail     refresh of that carry after a step of more than one token per request
 //   llark_seq_add_rmsnorm   x_out = x + rmsnorm(y) * w   (norm on the sublayer's output), optional ACT copy of x_out
+//   llark_seq_gated_norm_add  x_out = x + rmsnorm(y * sigmoid(gate)) * w, optional ACT copy of rmsnorm(x_out) * w_next
 //   llark_seq_rmsnorm_rows  y[i] = rmsnorm(x[rows[i]]) * w -> ACT (final norm of the rows whose logits are wanted)
 //   llark_seq_relu2         y = relu(u)^2
 //   llark_linear_rows       C = A W^T (+ bias) for a handful of rows: weight-streaming, one or two output columns per warp
@@ -274,6 +275,73 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ x, const float* __r
         x_out[row * C + c] = v;
         if (x_act) stf(x_act + row * C + c, v);
     }
+}
+
+// x_out = x + rmsnorm(y * sigmoid(gate)) * w, and optionally the NEXT sublayer's input norm in the same pass:
+// x_act = rmsnorm(x_out) * w_next -> T. gate (optional) is a column slice [rows, gate_ld] of a fused projection. The gated
+// row stays in shared memory between its reduction and its use, and is replaced there by the new stream for the second
+// norm. VEC: C % 4 == 0 and every row 16-byte aligned.
+__device__ __forceinline__ float sigmoid_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+template <typename T, bool VEC>
+__global__ void gated_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                                      const float* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
+                                      const float* __restrict__ w_next, float* __restrict__ x_out, T* __restrict__ x_act,
+                                      int C, float eps) {
+    extern __shared__ __align__(16) float rowbuf[];
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    const float* yr = y + row * C;
+    const float* gr = gate ? gate + row * gate_ld : nullptr;
+    const float* xr = x + row * C;
+    float* xo = x_out + row * C;
+    float ss = 0.f;
+    if constexpr (VEC) {
+        const int nv = C >> 2;
+        for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+            float4 a = reinterpret_cast<const float4*>(yr)[v];
+            if (gr) {
+                const float4 g = reinterpret_cast<const float4*>(gr)[v];
+                a.x *= sigmoid_(g.x), a.y *= sigmoid_(g.y), a.z *= sigmoid_(g.z), a.w *= sigmoid_(g.w);
+            }
+            reinterpret_cast<float4*>(rowbuf)[v] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    } else {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float a = yr[c];
+            if (gr) a *= sigmoid_(gr[c]);
+            rowbuf[c] = a;
+            ss = fmaf(a, a, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)C + eps);
+    float s2 = 0.f;
+    if constexpr (VEC) {
+        const int nv = C >> 2;
+        for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+            const float4 a = reinterpret_cast<float4*>(rowbuf)[v];
+            const float4 xv = reinterpret_cast<const float4*>(xr)[v], wv = reinterpret_cast<const float4*>(w)[v];
+            float4 o;
+            o.x = xv.x + a.x * r * wv.x, o.y = xv.y + a.y * r * wv.y, o.z = xv.z + a.z * r * wv.z, o.w = xv.w + a.w * r * wv.w;
+            reinterpret_cast<float4*>(xo)[v] = o;
+            reinterpret_cast<float4*>(rowbuf)[v] = o;
+            s2 += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+        }
+    } else {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            const float o = xr[c] + rowbuf[c] * r * w[c];
+            xo[c] = o;
+            rowbuf[c] = o;
+            s2 = fmaf(o, o, s2);
+        }
+    }
+    if (!x_act) return;
+    s2 = block_sum(s2, red);
+    const float r2 = 1.0f / sqrtf(s2 / (float)C + eps);
+    T* xa = x_act + row * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xa + c, rowbuf[c] * r2 * w_next[c]);  // each thread reads its own
 }
 
 template <typename T>
@@ -761,6 +829,40 @@ extern "C" int llark_seq_add_rmsnorm(const float* x, const float* y, const float
         add_rmsnorm_kernel<float><<<(unsigned)rows, th, 0, st>>>(x, y, w, x_out, (float*)x_act, C, eps);
     else
         add_rmsnorm_kernel<bf16_t><<<(unsigned)rows, th, 0, st>>>(x, y, w, x_out, (bf16_t*)x_act, C, eps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_gated_norm_add(const float* x, const float* y, const float* gate, long long gate_ld,
+                                        const float* w, const float* w_next, float* x_out, void* x_act, long long rows,
+                                        int C, float eps, int act_fp32, cudaStream_t st) {
+    if (rows <= 0 || C <= 0 || !x || !y || !w || !x_out || (x_act && !w_next)) return LLARK_EINVAL;
+    const size_t smem = sizeof(float) * (size_t)C;
+    if (smem > 200 * 1024) return LLARK_EINVAL;
+    const bool vec = (C % 4 == 0) && (!gate || gate_ld % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) &&
+                     ((uintptr_t)w % 16 == 0) && ((uintptr_t)x_out % 16 == 0) && (!gate || (uintptr_t)gate % 16 == 0);
+    int threads = vec ? C / 4 : C;
+    threads = threads < 64 ? 64 : (threads > 512 ? 512 : (threads + 31) / 32 * 32);
+#define LLARK_GNA(T, V)                                                                                               \
+    do {                                                                                                              \
+        if (smem > 48 * 1024) {                                                                                       \
+            cudaError_t e = cudaFuncSetAttribute(gated_norm_add_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 (int)smem);                                                          \
+            if (e != cudaSuccess) {                                                                                   \
+                g_last_cuda_error = (int)e;                                                                           \
+                return LLARK_ECUDA;                                                                                   \
+            }                                                                                                         \
+        }                                                                                                             \
+        gated_norm_add_kernel<T, V><<<(unsigned)rows, threads, smem, st>>>(x, y, gate, gate_ld, w, w_next, x_out,     \
+                                                                           (T*)x_act, C, eps);                       \
+    } while (0)
+    if (act_fp32) {
+        if (vec) LLARK_GNA(float, true);
+        else LLARK_GNA(float, false);
+    } else {
+        if (vec) LLARK_GNA(bf16_t, true);
+        else LLARK_GNA(bf16_t, false);
+    }
+#undef LLARK_GNA
     return check_launch();
 }
 

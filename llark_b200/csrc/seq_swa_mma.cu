@@ -46,7 +46,8 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
                const bf16_t* __restrict__ kring, const bf16_t* __restrict__ vring, const float* __restrict__ gate,
                long long gate_ld, const float* __restrict__ scale_h, bf16_t* __restrict__ out,
                const int* __restrict__ cu, const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G,
-               int D, int window, int cap, const float* __restrict__ sink, int gate_per_head) {
+               int D, int window, int cap, const float* __restrict__ sink, int gate_per_head, int chunk, float softcap,
+               const float* __restrict__ vfreq, int v_interleaved) {
     const int b = blockIdx.z, h = blockIdx.y;
     const int g = h / (H / G);
     const int row0 = cu[b], n = cu[b + 1] - row0;
@@ -70,9 +71,14 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
     }
     const int q_last = (qt0 + BQ - 1 < n - 1) ? qt0 + BQ - 1 : n - 1;
     const long long pq_lo = p0 + qt0, pq_hi = p0 + q_last;
-    const long long k_lo = pq_lo - window + 1 > 0 ? pq_lo - window + 1 : 0;
+    // first key any query of the tile sees: the start of the first query's block of `chunk` positions (blocks counted
+    // from position 0 of the sequence), or of its sliding window
+    const long long k_lo = chunk > 0 ? (pq_lo / chunk) * chunk : (pq_lo - window + 1 > 0 ? pq_lo - window + 1 : 0);
     const long long ring_base = (long long)slot[b] * cap;
-    const float sc = scale_h[h] * 1.4426950408889634f;  // scores in units of log2: softmax through exp2
+    constexpr float kLog2e = 1.4426950408889634f;
+    // scores in units of log2: softmax through exp2. With a soft cap the score is squashed first: cap tanh(s scale / cap)
+    const float sc = softcap > 0.f ? scale_h[h] / softcap : scale_h[h] * kLog2e;
+    const float cap2 = softcap * kLog2e;
 
     float o[DMAX / 8][4];
 #pragma unroll
@@ -153,31 +159,49 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
         }
         // ---- scale, mask (causal and window), online softmax in fp32
         float mt[2] = {-INFINITY, -INFINITY};
-        // rel = query position - first key of the tile: key column c is visible iff c <= rel and rel - c < window.
-        // A tile whose 64 keys are visible to all 16 rows of the warp (the usual case inside a wide window) skips the test.
+        // rel = query position - first key of the tile: key column c is visible iff lob <= c <= rel, where lob is the
+        // row's first visible position minus the tile's first key (window: rel - window + 1; chunk: start of the row's
+        // block). A tile whose 64 keys are visible to all 16 rows of the warp (the usual case inside a wide window)
+        // skips the test: the largest lob of the warp's rows is that of its last row.
         const long long rel_lo = pq_lo + warp * 16 - kt;  // rel of the warp's first row; its rows are consecutive
         const bool rows_ok = qt0 + warp * 16 + 15 < n;
-        const bool interior = rows_ok && rel_lo >= BK - 1 && rel_lo + 15 < window;
+        const long long p_last = pq_lo + warp * 16 + 15;
+        const long long lob_last = chunk > 0 ? (p_last / chunk) * chunk - kt : rel_lo + 15 - window + 1;
+        const bool interior = rows_ok && rel_lo >= BK - 1 && lob_last <= 0;
+        if (softcap > 0.f) {
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = cap2 * tanhf(s[nt][e] * sc);
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] *= sc;
+        }
         if (interior) {
 #pragma unroll
             for (int nt = 0; nt < BK / 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    s[nt][e] *= sc;
-                    mt[e >> 1] = fmaxf(mt[e >> 1], s[nt][e]);
-                }
+                for (int e = 0; e < 4; ++e) mt[e >> 1] = fmaxf(mt[e >> 1], s[nt][e]);
         } else {
             // clamp so that the 32-bit arithmetic below cannot overflow: beyond +-2^30 the answer is the same
-            const long long rl = rel_lo + gq;
-            const int rel0 = (int)(rl > (1LL << 30) ? (1LL << 30) : (rl < -(1LL << 30) ? -(1LL << 30) : rl));
+            auto clamp30 = [](long long v) { return (int)(v > (1LL << 30) ? (1LL << 30) : (v < -(1LL << 30) ? -(1LL << 30) : v)); };
+            int rel_x[2], lob_x[2];
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const long long rl = rel_lo + gq + x * 8;
+                rel_x[x] = clamp30(rl);
+                lob_x[x] = clamp30(chunk > 0 ? ((rl + kt) / chunk) * chunk - kt : rl - window + 1);
+            }
 #pragma unroll
             for (int nt = 0; nt < BK / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int x = e >> 1;
-                    const int rel = rel0 + x * 8, c = nt * 8 + 2 * tq + (e & 1);
-                    const bool ok = (qt0 + qrow + x * 8 < n) && c <= rel && rel - c < window;
-                    s[nt][e] = ok ? s[nt][e] * sc : -INFINITY;
+                    const int c = nt * 8 + 2 * tq + (e & 1);
+                    const bool ok = (qt0 + qrow + x * 8 < n) && c <= rel_x[x] && c >= lob_x[x];
+                    if (!ok) s[nt][e] = -INFINITY;
                     mt[x] = fmaxf(mt[x], s[nt][e]);
                 }
         }
@@ -239,8 +263,39 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
         if (qt0 + r >= n) continue;
         const long long trow = row0 + qt0 + r;
         // a sink adds exp(sink_h) to the denominator (m is in units of log2; every row has seen its own key, so m is finite)
-        const float inv = 1.0f / (sink ? l[x] + exp2f(sink[h] * 1.4426950408889634f - m[x]) : l[x]);
+        const float inv = 1.0f / (sink ? l[x] + exp2f(sink[h] * kLog2e - m[x]) : l[x]);
         const float gh = (gate && gate_per_head) ? 1.0f / (1.0f + expf(-gate[trow * gate_ld + h])) : 1.0f;
+        if (vfreq) {
+            // Values were stored rotated by their own position: the row's weighted sum is turned back by the query's
+            // position, pair mp by -p * vfreq[mp], before the gate. Interleaved pairs (2 mp, 2 mp + 1) are the two
+            // adjacent columns of one accumulator fragment; halves (mp, mp + D / 2) sit D / 16 fragments apart in the
+            // same thread (the launcher takes halves only when D = DMAX, so that the fragment index is a constant).
+            const float pf = (float)(p0 + qt0 + r);
+            if (v_interleaved) {
+#pragma unroll
+                for (int nt = 0; nt < DMAX / 8; ++nt)
+                    if (nt * 8 < D) {
+                        float si, co;
+                        sincosf(pf * vfreq[nt * 4 + tq], &si, &co);
+                        const float u = o[nt][2 * x], v = o[nt][2 * x + 1];
+                        o[nt][2 * x] = u * co + v * si;
+                        o[nt][2 * x + 1] = v * co - u * si;
+                    }
+            } else {
+                constexpr int hn = DMAX / 16;  // fragments per half
+#pragma unroll
+                for (int nt = 0; nt < hn; ++nt) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float si, co;
+                            sincosf(pf * vfreq[nt * 8 + 2 * tq + e], &si, &co);
+                            const float u = o[nt][2 * x + e], v = o[nt + hn][2 * x + e];
+                            o[nt][2 * x + e] = u * co + v * si;
+                            o[nt + hn][2 * x + e] = v * co - u * si;
+                        }
+                }
+            }
+        }
 #pragma unroll
         for (int nt = 0; nt < DMAX / 8; ++nt) {
             if (nt * 8 < D) {
@@ -261,7 +316,7 @@ template <int DMAX>
 static int launch(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                   const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu, const int* pos0,
                   const int* slot, int n_seq, int max_len, int H, int G, int D, int window, int cap, const float* sink,
-                  int gate_per_head, cudaStream_t st) {
+                  int gate_per_head, int chunk, float softcap, const float* vfreq, int v_interleaved, cudaStream_t st) {
     const size_t smem = sizeof(bf16_t) * (size_t)(BQ + 4 * BK) * (D + 8);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(swa_mma_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -273,7 +328,8 @@ static int launch(const void* qn, const void* kn, const void* vv, const void* kr
     dim3 grid((max_len + BQ - 1) / BQ, H, n_seq);
     swa_mma_kernel<DMAX><<<grid, 128, smem, st>>>((const bf16_t*)qn, (const bf16_t*)kn, (const bf16_t*)vv,
                                                   (const bf16_t*)kring, (const bf16_t*)vring, gate, gate_ld, scale_h,
-                                                  (bf16_t*)out, cu, pos0, slot, H, G, D, window, cap, sink, gate_per_head);
+                                                  (bf16_t*)out, cu, pos0, slot, H, G, D, window, cap, sink, gate_per_head,
+                                                  chunk, softcap, vfreq, v_interleaved);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         g_last_cuda_error = (int)e;
@@ -291,17 +347,19 @@ extern "C" int llark_seq_swa_attn_mma(const void* qn, const void* kn, const void
                                       const float* gate, long long gate_ld, const float* scale_h, void* out,
                                       const int* cu, const int* pos0, const int* slot, int n_seq, int max_len, int H,
                                       int G, int D, int window, int cap, const float* sink, int gate_per_head,
-                                      cudaStream_t st) {
+                                      int chunk, float softcap, const float* vfreq, int v_interleaved, cudaStream_t st) {
     if (n_seq <= 0 || max_len <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || (D % 16) || D > 256 || window <= 0 ||
-        cap <= 0 || !qn || !kn || !vv || !kring || !vring || !scale_h || !out || !cu || !pos0 || !slot)
+        cap <= 0 || !qn || !kn || !vv || !kring || !vring || !scale_h || !out || !cu || !pos0 || !slot || chunk < 0 ||
+        softcap < 0.f)
         return LLARK_EINVAL;
     if (gate && !gate_per_head && (gate_ld % 2)) return LLARK_EINVAL;
+    if (vfreq && !v_interleaved && D != 64 && D != 128 && D != 256) return LLARK_EINVAL;
     if (D <= 64)
         return swamma::launch<64>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len, H,
-                                  G, D, window, cap, sink, gate_per_head, st);
+                                  G, D, window, cap, sink, gate_per_head, chunk, softcap, vfreq, v_interleaved, st);
     if (D <= 128)
         return swamma::launch<128>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len,
-                                   H, G, D, window, cap, sink, gate_per_head, st);
+                                   H, G, D, window, cap, sink, gate_per_head, chunk, softcap, vfreq, v_interleaved, st);
     return swamma::launch<256>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len, H, G,
-                               D, window, cap, sink, gate_per_head, st);
+                               D, window, cap, sink, gate_per_head, chunk, softcap, vfreq, v_interleaved, st);
 }

@@ -31,6 +31,19 @@ the same packed weights and stores of its own.
                                         ranked by their best), weights = plain scores, and trailing experts without
                                         weights that hand their input through
 
+    "rotary_attention"  RotaryAttention   grouped-query softmax attention with rotary positions on q and k (halves or
+                                        interleaved pairs, part of the head, optionally rescaled frequencies), optional
+                                        soft cap of the scores, a mask by blocks of positions (or a window, or none: the
+                                        keys then live in per-position stores), element-wise sigmoid gate
+    "rotary_attention_vrot"  ValueRotaryAttention   the same with biased projections, an RMS norm over the WHOLE q and k
+                                        projections, interleaved pairs, values that are stored rotated by their own position
+                                        (the head outputs are turned back by the query's) and a 1 in every softmax denominator
+    "latent_attention_causal"  LatentCausalAttention   latent attention over everything before (per-position store), rotary
+                                        halves, one gate per head
+
+Mixers that take `side=(matrix name, bias name)` compute that projection of their input inside their fused input GEMM and
+leave it in `self.side` (fp32 view) after forward(): a layer's gate on the sublayer's result reads the same input.
+
 A mixer's `branches(x_act, st, cache)` returns ([(output fp32, norm weight or None), ...], scale): what the layer's residual
 kernel adds up (each output first RMS-normed with its weight when there is one). The default is the one output of forward().
 """
@@ -166,6 +179,9 @@ class ReluSquaredFF:
         return ops.linear(ops.seq_relu2(u), self.w.w_down, out_dtype=F32)
 
 
+WINDOW_ALL = 1 << 30  # "window" of an attention that sees every earlier position
+
+
 def _expect(pfx, pairs):
     for t, shape in pairs:
         if tuple(t.shape) != tuple(shape):
@@ -173,8 +189,8 @@ def _expect(pfx, pairs):
 
 
 def rotary_frequencies(dims, base, scaling=None):
-    """f_i = base^(-2i/dims), i < dims/2 (float64), blended the YaRN way when `scaling` = {factor, original, fast, slow}
-    is given: with where(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(where(fast)), 0),
+    """f_i = base^(-2i/dims), i < dims/2 (float64). `scaling` = {factor, original, low, high}: rescaled in three bands of
+    the wavelength (see below). `scaling` = {factor, original, fast, slow}: blended the YaRN way: with where(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(where(fast)), 0),
     hi = min(ceil(where(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
     f_i / factor * ramp_i + f_i (1 - ramp_i); cos and sin are then multiplied by 0.1 ln(factor) + 1. Returns
     (frequencies as a float64 tensor, that multiplier)."""
@@ -183,6 +199,14 @@ def rotary_frequencies(dims, base, scaling=None):
     if not scaling:
         return f, 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
+    if "low" in scaling or "high" in scaling:
+        # rescaling in three bands of the wavelength l = 2 pi / f: l < original / high keeps f, l > original / low gets
+        # f / factor, between them s = (original / l - low) / (high - low) blends (1 - s) f / factor + s f
+        low, high = float(scaling["low"]), float(scaling["high"])
+        wave = 2.0 * math.pi / f
+        s = ((original / wave - low) / (high - low)).clamp(0.0, 1.0) if high != low else torch.zeros_like(f)
+        mid = (1.0 - s) * f / factor + s * f
+        return torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, mid)), 1.0
 
     def where(turns):
         return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
@@ -194,10 +218,14 @@ def rotary_frequencies(dims, base, scaling=None):
 
 
 class LatentWindowAttentionWeights:
-    def __init__(self, w, pfx, spec, width, dev, act):
+    halves = False         # rotary pairs (i, i + n/2) instead of (2i, 2i + 1)
+    gate_per_head = False  # the gate projection has one row per head instead of one per output channel
+
+    def __init__(self, w, pfx, spec, width, dev, act, side=None):
         H, Dn, P, E, R = (int(spec[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank"))
         self.H, self.Dn, self.P, self.E, self.R = H, Dn, P, E, R
-        self.window = int(spec["mask"]["size"])
+        mask = spec.get("mask") or {}
+        self.window = int(mask["size"]) if mask.get("size") else None  # None: every earlier position
         rot = spec.get("rot") or {}
         n_rot = int(rot.get("dims", P))
         if n_rot % 2 or n_rot > P:
@@ -207,13 +235,26 @@ class LatentWindowAttentionWeights:
             self.freqs = f.to(device=dev, dtype=F32).contiguous()
         else:
             self.freqs, self.mult = None, 1.0
-        # one projection for q | latent + shared rotated key part | gate
-        self.w_in = torch.cat([_mat(w, pfx + "q", dev, act), _mat(w, pfx + "dkv", dev, act), _mat(w, pfx + "g", dev, act)])
-        self.q_n, self.lat_off, self.g_off = H * (Dn + P), H * (Dn + P), H * (Dn + P) + R + P
+        # one projection for (side |) q | latent + shared rotated key part | gate
+        n_gate = H if self.gate_per_head else H * E
+        parts = [_mat(w, pfx + "q", dev, act), _mat(w, pfx + "dkv", dev, act), _mat(w, pfx + "g", dev, act)]
+        _expect(pfx, ((parts[0], (H * (Dn + P), width)), (parts[1], (R + P, width)), (parts[2], (n_gate, width))))
+        self.side_n, self.b_in = 0, None
+        if side is not None:
+            parts.insert(0, _mat(w, side[0], dev, act))
+            self.side_n = parts[0].shape[0]
+            _expect(pfx, ((parts[0], (self.side_n, width)),))
+        self.q_off = self.side_n
+        self.q_n, self.lat_off = H * (Dn + P), self.q_off + H * (Dn + P)
+        self.g_off = self.lat_off + R + P
+        self.n_in = self.g_off + n_gate
+        self.w_in = _pad_rows(torch.cat(parts))
+        if side is not None and side[1] is not None:
+            self.b_in = torch.zeros(self.w_in.shape[0], device=dev, dtype=F32)
+            self.b_in[:self.side_n] = _vec(w, side[1], dev)
         self.norm = _vec(w, pfx + "dkv.norm", dev)
         uk, uv = _mat(w, pfx + "uk", dev, act), _mat(w, pfx + "uv", dev, act)
-        _expect(pfx, ((self.w_in, (H * (Dn + P) + R + P + H * E, width)), (uk, (H * Dn, R)), (uv, (H * E, R)),
-                      (self.norm, (R,))))
+        _expect(pfx, ((uk, (H * Dn, R)), (uv, (H * E, R)), (self.norm, (R,))))
         self.uk_t = uk.view(H, Dn, R).transpose(1, 2).contiguous()  # [H, R, Dn]: folds W_uk into the query
         self.uv = uv.view(H, E, R).contiguous()                     # [H, E, R]: unfolds the latent-space output
         self.scale_h = torch.full((H,), float(spec["scale"]), device=dev, dtype=F32)
@@ -226,28 +267,46 @@ class LatentWindowAttention:
 
     def __init__(self, weights, cache, eps, act, max_positions=None):
         self.w, self.eps, self.act = weights, float(eps), act
+        self.side = None
         w = weights
-        self.cap = max(1, min(w.window, int(max_positions))) if max_positions else max(1, w.window)
-        self.h_ring = cache.add_store((self.cap, w.R + w.P), act, zero_on_alloc=False)
+        if w.window is None:  # one entry per position, grown by the cache
+            self.cap = None
+            self.h_ring = cache.add_store((w.R + w.P,), act, zero_on_alloc=False, per_position=True)
+        else:
+            self.cap = max(1, min(w.window, int(max_positions))) if max_positions else max(1, w.window)
+            self.h_ring = cache.add_store((self.cap, w.R + w.P), act, zero_on_alloc=False)
 
     def forward(self, hc, st, cache):
         w = self.w
         W = w.R + w.P
         ring = cache.view(self.h_ring)
-        pin = ops.linear(hc, w.w_in, out_dtype=F32)
-        q, lat, gate = pin[:, :w.q_n], pin[:, w.lat_off:w.g_off], pin[:, w.g_off:]
+        cap = self.cap if self.cap is not None else cache.positions
+        pin = ops.linear(hc, w.w_in, bias=w.b_in, out_dtype=F32)
+        self.side = pin[:, :w.side_n] if w.side_n else None
+        q, lat, gate = pin[:, w.q_off:w.lat_off], pin[:, w.lat_off:w.g_off], pin[:, w.g_off:w.n_in]
         single = st.max_len == 1
         ckr, qf = ops.seq_latent_prep(q, lat, w.norm, w.freqs, w.mult, st, w.H, w.Dn, w.P, w.R, self.eps, self.act,
-                                      ring=ring if single else None, cap=self.cap)
+                                      ring=ring if single else None, cap=cap, halves=w.halves)
         ops.seq_head_linear(q, w.Dn + w.P, w.uk_t, qf, W, N=w.R, K=w.Dn)
-        # one shared key head whose rows [latent | rotated part] are also the values; output columns >= R are unused
-        o = ops.seq_swa_attn(qf, ckr, ckr, ring, ring, None, 0, w.scale_h, st, w.H, 1, W, W, w.window, self.cap,
-                             from_ring_only=single)
+        # one shared key head whose rows [latent | rotated part] are also the values; output columns >= R are unused. A
+        # gate of one number per head commutes with the unfolding and is applied here, an element-wise one after it.
+        o = ops.seq_swa_attn(qf, ckr, ckr, ring, ring, gate if w.gate_per_head else None,
+                             pin.stride(0) if w.gate_per_head else 0, w.scale_h, st, w.H, 1, W, W,
+                             w.window or WINDOW_ALL, cap, from_ring_only=single, gate_per_head=w.gate_per_head)
         if not single:
-            ops.seq_kv_ring_write(ckr, None, ring, None, st, self.cap)
+            ops.seq_kv_ring_write(ckr, None, ring, None, st, cap)
         og = torch.empty((st.n_tok, w.H * w.E), device=hc.device, dtype=self.act)
-        ops.seq_head_linear(o, W, w.uv, og, w.E, N=w.E, K=w.R, gate=gate)
+        ops.seq_head_linear(o, W, w.uv, og, w.E, N=w.E, K=w.R, gate=None if w.gate_per_head else gate)
         return ops.linear(og, w.w_o, out_dtype=F32)
+
+
+class LatentCausalAttentionWeights(LatentWindowAttentionWeights):
+    halves = True
+    gate_per_head = True
+
+
+class LatentCausalAttention(LatentWindowAttention):
+    Weights = LatentCausalAttentionWeights
 
 
 class GatedDeltaRuleWeights:
@@ -386,9 +445,6 @@ class ScalarGatedDeltaRule(_OneBranch):
         return ops.linear(on, w.w_o, out_dtype=F32)
 
 
-WINDOW_ALL = 1 << 30  # "window" of an attention that sees every earlier position
-
-
 class SinkAttentionWeights:
     def __init__(self, w, pfx, spec, width, dev, act):
         H, D = int(spec["heads"]), int(spec["dim"])
@@ -448,6 +504,121 @@ class SinkAttention(_OneBranch):
         if not single:
             ops.seq_kv_ring_write(kn, vv, kring, vring, st, cap)
         return ops.linear(o, w.w_o, out_dtype=F32)
+
+
+class RotaryAttentionWeights:
+    biases = False            # q, k and v projections have biases (`<name>.b`)
+    whole_norm = False        # RMS norm over the whole q and k projections (weights `q.norm`, `k.norm`) before rotation
+    interleaved = False       # rotary pairs (2i, 2i + 1) instead of (i, i + n/2)
+    rotate_values = False     # values are stored rotated by their position over all of vdim; outputs are turned back
+    plus_one = False          # a 1 joins every softmax denominator (a key of score 0 without a value)
+    mask_kind = "chunk"       # what mask.size means: "chunk" = blocks of positions counted from 0, "window" = sliding
+
+    def __init__(self, w, pfx, spec, width, dev, act, side=None):
+        H, D = int(spec["heads"]), int(spec["dim"])
+        G, E = int(spec.get("kv_heads", H)), int(spec.get("vdim", D))
+        if H % G:
+            raise ValueError(f"{pfx}: heads must be a multiple of kv_heads")
+        self.H, self.G, self.D, self.E = H, G, D, E
+        mask = spec.get("mask") or {}
+        self.span = int(mask["size"]) if mask.get("size") else None  # None: every earlier position
+        if self.span is not None and self.span <= 0:
+            raise ValueError(f"{pfx}: mask.size must be positive")
+        cap = spec.get("softcap")
+        self.softcap = float(cap) if cap else 0.0
+        rot = spec.get("rot") or {}
+        n_rot = int(rot.get("dims", D)) if rot else 0
+        if n_rot % 2 or n_rot > D:
+            raise ValueError(f"{pfx}: rot.dims must be even and at most dim")
+        self.qk_freq = None
+        if n_rot:
+            f, mult = rotary_frequencies(n_rot, rot["base"], rot.get("scaling"))
+            if mult != 1.0:
+                raise ValueError(f"{pfx}: this mixer takes no magnitude factor on the rotation")
+            self.qk_freq = f.to(device=dev, dtype=F32).contiguous()
+        self.v_freq = None
+        if self.rotate_values:
+            if E % 2:
+                raise ValueError(f"{pfx}: rotated values need an even vdim")
+            self.v_freq = rotary_frequencies(E, rot["base"])[0].to(device=dev, dtype=F32).contiguous()
+        # one projection for (side |) q | k | v | gate
+        names = ("q", "k", "v", "g")
+        parts = [_mat(w, pfx + n, dev, act) for n in names]
+        _expect(pfx, ((parts[0], (H * D, width)), (parts[1], (G * D, width)), (parts[2], (G * E, width)),
+                      (parts[3], (H * E, width))))
+        bias = [(_vec(w, pfx + n + ".b", dev) if self.biases and n != "g" else torch.zeros(m.shape[0], device=dev, dtype=F32))
+                for n, m in zip(names, parts)]
+        self.side_n = 0
+        if side is not None:
+            parts.insert(0, _mat(w, side[0], dev, act))
+            self.side_n = parts[0].shape[0]
+            _expect(pfx, ((parts[0], (self.side_n, width)),))
+            bias.insert(0, _vec(w, side[1], dev) if side[1] is not None else torch.zeros(self.side_n, device=dev, dtype=F32))
+        self.q_off = self.side_n
+        self.k_off, self.v_off, self.g_off = self.q_off + H * D, self.q_off + (H + G) * D, self.q_off + (H + G) * D + G * E
+        self.n_in = self.g_off + H * E
+        self.w_in = _pad_rows(torch.cat(parts))
+        self.b_in = None
+        if self.biases or (side is not None and side[1] is not None):
+            self.b_in = torch.zeros(self.w_in.shape[0], device=dev, dtype=F32)
+            self.b_in[:self.n_in] = torch.cat(bias)
+        self.q_norm = self.k_norm = None
+        if self.whole_norm:
+            self.q_norm, self.k_norm = _vec(w, pfx + "q.norm", dev), _vec(w, pfx + "k.norm", dev)
+            _expect(pfx, ((self.q_norm, (H * D,)), (self.k_norm, (G * D,))))
+        self.sink = torch.zeros(H, device=dev, dtype=F32) if self.plus_one else None  # exp(0) in the denominator
+        self.scale_h = torch.full((H,), float(spec["scale"]), device=dev, dtype=F32)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        _expect(pfx, ((self.w_o, (width, H * E)),))
+
+
+class RotaryAttention(_OneBranch):
+    Weights = RotaryAttentionWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        self.side = None
+        w = weights
+        if w.span is None:  # one entry per position, grown by the cache
+            self.ring = None
+            self.h_k = cache.add_store((w.G * w.D,), act, zero_on_alloc=False, per_position=True)
+            self.h_v = cache.add_store((w.G * w.E,), act, zero_on_alloc=False, per_position=True)
+        else:  # the keys a query sees never outnumber mask.size: a ring, entry = position % size
+            self.ring = max(1, min(w.span, int(max_positions))) if max_positions else w.span
+            self.h_k = cache.add_store((self.ring, w.G * w.D), act, zero_on_alloc=False)
+            self.h_v = cache.add_store((self.ring, w.G * w.E), act, zero_on_alloc=False)
+
+    def forward(self, hc, st, cache):
+        w = self.w
+        pin = ops.linear(hc, w.w_in, bias=w.b_in, out_dtype=F32)
+        self.side = pin[:, :w.side_n] if w.side_n else None
+        kring, vring = cache.view(self.h_k), cache.view(self.h_v)
+        cap = self.ring if self.ring is not None else cache.positions
+        single = st.max_len == 1
+        q, k, v = ops.seq_qkv_rotary(pin, w.q_off, w.k_off, w.v_off, w.H, w.G, w.D, w.E, self.eps, self.act, st,
+                                     wq=w.q_norm, wk=w.k_norm, qk_freq=w.qk_freq, qk_interleaved=w.interleaved,
+                                     v_freq=w.v_freq, v_interleaved=w.interleaved,
+                                     kring=kring if single else None, vring=vring if single else None, cap=cap)
+        chunk = w.span if (w.span is not None and w.mask_kind == "chunk") else 0
+        window = w.span if (w.span is not None and w.mask_kind == "window") else WINDOW_ALL
+        o = ops.seq_swa_attn(q, k, v, kring, vring, pin[:, w.g_off:w.n_in], pin.stride(0), w.scale_h, st, w.H, w.G, w.D,
+                             w.E, window, cap, from_ring_only=single, sink=w.sink, chunk=chunk, softcap=w.softcap,
+                             vfreq=w.v_freq, v_interleaved=w.interleaved)
+        if not single:
+            ops.seq_kv_ring_write(k, v, kring, vring, st, cap)
+        return ops.linear(o, w.w_o, out_dtype=F32)
+
+
+class ValueRotaryAttentionWeights(RotaryAttentionWeights):
+    biases = True
+    whole_norm = True
+    interleaved = True
+    rotate_values = True
+    plus_one = True
+
+
+class ValueRotaryAttention(RotaryAttention):
+    Weights = ValueRotaryAttentionWeights
 
 
 class StateSpaceDualityWeights:
@@ -628,6 +799,8 @@ class BiasedSoftmaxExperts(RoutedExperts):
 
 MIXERS = {"attention": GatedWindowAttention, "hgrn2": GatedLinearRecurrence, "latent_attention": LatentWindowAttention,
           "channel_delta": GatedDeltaRule, "general_delta": GeneralizedDeltaRule, "delta": ScalarGatedDeltaRule,
-          "sink_attention": SinkAttention, "ssd": StateSpaceDuality, "parallel": ParallelMixers}
+          "sink_attention": SinkAttention, "ssd": StateSpaceDuality, "parallel": ParallelMixers,
+          "rotary_attention": RotaryAttention, "rotary_attention_vrot": ValueRotaryAttention,
+          "latent_attention_causal": LatentCausalAttention}
 FEED_FORWARDS = {"dense": ReluSquaredFF, "moe": RoutedExperts, "clamped_glu": ClampedGluFF,
                  "moe_softmax_bias": BiasedSoftmaxExperts}

@@ -21,6 +21,7 @@ def register_native(architecture, module, class_name):
 register_native("Kelutar", "llark_b200.models.kelutar", "KelutarForCausalLM")
 register_native("Golavik", "llark_b200.models.golavik", "GolavikForCausalLM")
 register_native("Gubulorn", "llark_b200.models.gubulorn", "GubulornForCausalLM")
+register_native("Tokatar", "llark_b200.models.tokatar", "TokatarForCausalLM")
 
 
 def read_config(folder):

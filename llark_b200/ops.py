@@ -550,6 +550,25 @@ def seq_add_rmsnorm(x, y, w, eps, act=None):
     return (out, xa) if act is not None else out
 
 
+def seq_gated_norm_add(x, y, w, eps, gate=None, w_next=None, act=None):
+    """x + rmsnorm(y * sigmoid(gate)) * w (fp32, new tensor; gate fp32, a column slice is fine); with w_next also
+    rmsnorm(result) * w_next in `act`: the input of the next sublayer."""
+    _req(x, torch.float32), _req(y, torch.float32), _req(w, torch.float32)
+    rows, C = x.shape
+    if not y.is_contiguous() or y.shape != x.shape:
+        raise ValueError("seq_gated_norm_add: y must be contiguous and of the stream's shape")
+    if gate is not None:
+        _req(gate, torch.float32)
+        if gate.shape != x.shape or gate.stride(1) != 1:
+            raise ValueError("seq_gated_norm_add: gate must be [rows, C] with unit column stride")
+    out = torch.empty_like(x)
+    xa = torch.empty((rows, C), device=x.device, dtype=act) if w_next is not None else None
+    check(lib().llark_seq_gated_norm_add(_p(x), _p(y), _p(gate), gate.stride(0) if gate is not None else 0, _p(w),
+                                         _p(w_next), _p(out), _p(xa), rows, C, float(eps),
+                                         _actf(act) if w_next is not None else 0, _stream()), "seq_gated_norm_add")
+    return (out, xa) if w_next is not None else out
+
+
 def seq_rmsnorm_rows(x, rows, w, eps, act):
     _req(x, torch.float32), _req(w, torch.float32)
     n = rows.numel() if rows is not None else x.shape[0]
@@ -601,24 +620,56 @@ SWA_MMA_MIN_LEN = 16  # shortest longest-request of a step that goes to the tens
 
 
 def seq_swa_attn(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, st, H, G, D, E, window, cap, from_ring_only, sink=None,
-                 gate_per_head=False):
+                 gate_per_head=False, chunk=0, softcap=0.0, vfreq=None, v_interleaved=False):
     """Softmax attention of a packed step over the last `window` positions (rings of `cap` entries per slot hold what
-    earlier steps brought). sink fp32 [H]: one more term exp(sink_h) of the denominator; gate_per_head: gate [n_tok, H]."""
+    earlier steps brought). sink fp32 [H]: one more term exp(sink_h) of the denominator; gate_per_head: gate [n_tok, H].
+    chunk > 0: instead of the window the query sees the earlier positions of its own block of `chunk` positions (blocks
+    counted from position 0 of the sequence). softcap > 0: score <- softcap * tanh(score / softcap). vfreq fp32 [E / 2]:
+    the values were stored rotated by their own position; each head's weighted sum is turned back by the query's."""
     out = torch.empty((st.n_tok, H * E), device=qn.device, dtype=qn.dtype)
     if sink is not None:
         _req(sink, torch.float32)
+    if vfreq is not None:
+        _req(vfreq, torch.float32)
+        if vfreq.numel() != E // 2:
+            raise ValueError("seq_swa_attn: one frequency per pair of value channels")
     if (qn.dtype == BF16 and not from_ring_only and st.max_len >= SWA_MMA_MIN_LEN and D == E and D % 16 == 0
-            and D <= 256 and (gate_per_head or gate_ld % 2 == 0)):
+            and D <= 256 and (gate is None or gate_per_head or gate_ld % 2 == 0)
+            and (vfreq is None or v_interleaved or D in (64, 128, 256))):
         # prompts and portions: 64-query tiles on the tensor cores; single tokens, fp32 and odd head sizes stay SIMT
         check(lib().llark_seq_swa_attn_mma(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h),
                                            _p(out), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_seq, st.max_len, H, G, D,
-                                           window, cap, _p(sink), int(gate_per_head), _stream()), "seq_swa_attn_mma")
+                                           window, cap, _p(sink), int(gate_per_head), int(chunk), float(softcap or 0.0),
+                                           _p(vfreq), int(v_interleaved), _stream()), "seq_swa_attn_mma")
         return out
     check(lib().llark_seq_swa_attn(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h), _p(out),
                                    _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_tok, H, G, D, E, window, cap,
-                                   int(from_ring_only), _p(sink), int(gate_per_head), _actf(qn.dtype), _stream()),
+                                   int(from_ring_only), _p(sink), int(gate_per_head), int(chunk), float(softcap or 0.0),
+                                   _p(vfreq), int(v_interleaved), _actf(qn.dtype), _stream()),
           "seq_swa_attn")
     return out
+
+
+def seq_qkv_rotary(src, q_off, k_off, v_off, H, G, D, E, eps, act, st, wq=None, wk=None, qk_freq=None, qk_interleaved=False,
+                   v_freq=None, v_interleaved=False, kring=None, vring=None, cap=0):
+    """src fp32 [n_tok, ld] -> (q [n_tok, H*D], k [n_tok, G*D], v [n_tok, G*E]) in `act`. wq / wk: RMS norm over the whole
+    q / k projection with weights [H*D] / [G*D]. qk_freq fp32 [n_rot / 2]: the first n_rot entries of each q / k head are
+    rotated by position * frequency (pairs (i, i + n_rot/2), or (2i, 2i+1) when interleaved). v_freq fp32 [E / 2]: the
+    value heads are rotated the same way over all of E. With kring / vring the k / v rows also go straight into the rings
+    (steps of one token per request)."""
+    _req(src, torch.float32)
+    n = src.shape[0]
+    qn = torch.empty((n, H * D), device=src.device, dtype=act)
+    kn = torch.empty((n, G * D), device=src.device, dtype=act)
+    vv = torch.empty((n, G * E), device=src.device, dtype=act)
+    n_rot = 2 * qk_freq.numel() if qk_freq is not None else 0
+    if v_freq is not None and v_freq.numel() != E // 2:
+        raise ValueError("seq_qkv_rotary: one frequency per pair of value channels")
+    check(lib().llark_seq_qkv_rotary(_p(src), src.stride(0), q_off, k_off, v_off, _p(wq), _p(wk), _p(qk_freq), n_rot,
+                                     int(qk_interleaved), _p(v_freq), int(v_interleaved), _p(qn), _p(kn), _p(vv), _p(kring),
+                                     _p(vring), _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), n, H, G, D, E, int(cap),
+                                     float(eps), _actf(act), _stream()), "seq_qkv_rotary")
+    return qn, kn, vv
 
 
 def seq_kv_ring_write(kn, vv, kring, vring, st, cap):
@@ -804,10 +855,11 @@ def seq_logit_cap_(z, scale, cap):
     return z
 
 
-def seq_latent_prep(q, lat, norm_w, freqs, mult, st, H, Dn, P, R, eps, act, ring=None, cap=0):
+def seq_latent_prep(q, lat, norm_w, freqs, mult, st, H, Dn, P, R, eps, act, ring=None, cap=0, halves=False):
     """q fp32 [n_tok, H*(Dn+P)], lat fp32 [n_tok, R+P] (column slices fine) -> ckr act [n_tok, R+P] (normed latent |
     rotated shared key part) and qf act [n_tok, H, R+P] with columns R.. = rotated query parts (columns < R are left
-    for seq_head_linear). With `ring` the ckr rows also go to the ring entries of the tokens' positions."""
+    for seq_head_linear). With `ring` the ckr rows also go to the ring entries of the tokens' positions. Rotary pairs are
+    (2i, 2i + 1), or (i, i + n_rot / 2) with `halves`."""
     n = st.n_tok
     ckr = torch.empty((n, R + P), device=q.device, dtype=act)
     qf = torch.empty((n, H * (R + P)), device=q.device, dtype=act)
@@ -815,7 +867,7 @@ def seq_latent_prep(q, lat, norm_w, freqs, mult, st, H, Dn, P, R, eps, act, ring
     check(lib().llark_seq_latent_prep(_p(_req(q, torch.float32)), q.stride(0), _p(_req(lat, torch.float32)),
                                       lat.stride(0), _p(norm_w), _p(freqs), n_rot, float(mult), _p(ckr), _p(qf), _p(ring),
                                       _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), n, H, Dn, P, R, int(cap),
-                                      float(eps), _actf(act), _stream()), "seq_latent_prep")
+                                      float(eps), int(halves), _actf(act), _stream()), "seq_latent_prep")
     return ckr, qf
 
 
