@@ -51,7 +51,7 @@ def save_file(tensors, path, metadata=None):
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
     for name, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""  # a single number has no axis to view
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
         blobs.append(raw)
         at += len(raw)
