@@ -59,13 +59,14 @@ def parse():
                     help="skip the configs[1] (Jukebox only) and configs[3] (end-to-end) measurements added to the line")
     ap.add_argument("--no-torch-baseline", action="store_true",
                     help="skip the stock-PyTorch run of the reference's model class on the same GPU (N=1 only)")
-    ap.add_argument("--workload", default="llama", choices=["llama", "e2e", "generation", "generation-golavik", "generation-gubulorn"],
+    ap.add_argument("--workload", default="llama", choices=["llama", "e2e", "generation", "generation-golavik", "generation-gubulorn", "generation-tokatar"],
                     help="llama = BASELINE configs[2] (precomputed Jukebox embeds, the default headline); "
                          "e2e = configs[3]: 25 s waveform -> Jukebox front end -> projector -> Llama step in-process; "
                          "generation = prefill / decode tokens/s of the Kelutar decoder beside the Llama path at equal "
                          "size, with a per-op roofline table (N = 1; llark_b200/bench_generation.py); "
                          "generation-golavik = the same for the Golavik decoder beside Kelutar at equal size; "
-                         "generation-gubulorn = the same for the Gubulorn decoder beside Golavik at equal size")
+                         "generation-gubulorn = the same for the Gubulorn decoder beside Golavik at equal size; "
+                         "generation-tokatar = the same for the Tokatar decoder beside an all-attention Kelutar at equal size")
     ap.add_argument("--jukebox-precision", default="bf16", choices=["bf16", "tf32"])
     return ap.parse_args()
 
@@ -616,6 +617,13 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         pk, kind = peaks()
         bench_generation.run_gubulorn(args, pk, kind, emit)
+        return
+    if args.workload == "generation-tokatar":
+        from llark_b200 import bench_generation
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        pk, kind = peaks()
+        bench_generation.run_tokatar(args, pk, kind, emit)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -1,5 +1,6 @@
 """Generation throughput of the Kelutar path beside the Llama path at equal size (`bench.py --workload generation`), of
-Golavik beside Kelutar (`generation-golavik`) and of Gubulorn beside Golavik (`generation-gubulorn`).
+Golavik beside Kelutar (`generation-golavik`), of Gubulorn beside Golavik (`generation-gubulorn`) and of Tokatar beside an
+all-attention Kelutar (`generation-tokatar`).
 
 Random weights, synthetic token ids. For each size: prefill tokens/s (a packed batch of whole prompts) and decode tokens/s
 (one token per request and step, after a prompt of `context` tokens) for both decoders, plus a per-op table: every op
@@ -167,6 +168,11 @@ def _op_work(name, a, k, out, ctx):
         return _nbytes(x) + N * K * w.element_size() + _nbytes(out), 2.0 * M * N * K
     if name == "seq_swa_attn":
         qn, st, H, G, D, E, window = a[0], a[8], a[9], a[10], a[11], a[12], a[13]
+        chunk = k.get("chunk") or 0
+        if chunk:  # a query sees its own block of positions up to itself; the step reads its blocks' keys once
+            keys = sum((p0 + i) % chunk + 1 for p0, n in zip(st.pos0_host, st.lens) for i in range(n))
+            kv_once = sum(n + min(p0 % chunk, p0) for p0, n in zip(st.pos0_host, st.lens)) * G * (D + E) * 2
+            return 2 * _nbytes(qn) + kv_once + st.n_tok * H * E * 4, 2.0 * keys * H * (D + E)
         keys = sum(min(window, p0 + i + 1) for p0, n in zip(st.pos0_host, st.lens) for i in range(n))
         kv_once = sum(min(n + min(window, p0), n + window) for p0, n in zip(st.pos0_host, st.lens)) * G * (D + E) * 2
         return 2 * _nbytes(qn) + kv_once + st.n_tok * H * E * 4, 2.0 * keys * H * (D + E)
@@ -198,6 +204,8 @@ def _op_work(name, a, k, out, ctx):
         return _nbytes(a[0]) + _nbytes(out), 0.0
     if name == "seq_qk_headnorm":
         return _nbytes(a[0]) * 2 // 3 + _nbytes(out), 0.0
+    if name == "seq_qkv_rotary":  # reads the q | k | v columns of the fused projection, writes them in the activation dtype
+        return 3 * _nbytes(out), 0.0
     if name == "seq_kv_ring_write":
         return 2 * (_nbytes(a[0]) + _nbytes(a[1])), 0.0
     if name == "embed_splice_fwd":
@@ -512,6 +520,128 @@ def run_gubulorn(args, peaks, peaks_kind, emit):
           "warmup": max(args.warmup, 3), "ms_per_step": head["prefill"]["gubulorn_ms"], "higher_is_better": True,
           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
           "config": {"model": "Gubulorn " + head["size"], "l2": "256 MB fill between timed steps",
+                     "peaks": peaks_kind, "hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]},
+          "sizes": results, "wall_s": round(time.time() - t0, 1)})
+
+
+TOKATAR_OPS = ["linear", "seq_embed", "seq_group_rmsnorm", "seq_gated_norm_add", "seq_relu2", "seq_qkv_rotary", "seq_swa_attn",
+               "seq_kv_ring_write", "seq_latent_prep", "seq_head_linear"]
+
+# (name, width, layers, heads, key/value heads, head dim, block of positions, ff, latent rank, rotated size, vocab): layers
+# repeat attention, attention_2, latent_attention, attention, each with a dense feed-forward; the Kelutar model beside it has
+# an attention layer with the same feed-forward in EVERY place (same width, layer count, heads, key / value heads, and a
+# window as long as the block)
+TOKATAR_SIZES = [
+    ("t2048", 2048, 8, 16, 4, 128, 2048, 8192, 192, 64, 32000),
+    ("t4096", 4096, 4, 32, 8, 128, 2048, 11008, 192, 64, 32000),
+]
+
+
+def tokatar_config(width, layers, heads, kv, dim, block, ff, rank, rot, vocab):
+    mlp = {"kind": "dense", "ff": ff}
+    scale = 1.0 / math.sqrt(dim)
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": block}, "scale": scale,
+                     "softcap": 50.0, "rot": {"base": 250000.0, "dims": dim,
+                                              "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
+    att2 = {"type": "attention_2", "mlp": mlp,
+            "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "mask": {"size": block}, "scale": scale,
+                      "rot": {"base": 500000.0, "dims": dim}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank,
+                     "scale": 1.0 / math.sqrt(dim + rot), "rot": {"base": 20000.0, "dims": rot}}}
+    return {"architecture": "Tokatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": math.sqrt(width)}, "layers": [(att, att2, lat, att)[i % 4] for i in range(layers)]}
+
+
+def tokatar_random_weights(cfg, device, seed=0):
+    g = torch.Generator(device=device).manual_seed(seed)
+    C = cfg["width"]
+
+    def mat(o, i, s=None):
+        return (torch.randn(o, i, device=device, generator=g) * (s or 1.0 / math.sqrt(i))).to(BF16)
+
+    def vec(n, mean=1.0, s=0.1):
+        return (mean + torch.randn(n, device=device, generator=g) * s).to(BF16)
+
+    def one(mean=1.0):
+        return vec(1, mean).reshape(())
+
+    W = {"embed": mat(cfg["vocab"], C, 1.0 / math.sqrt(C)), "final.norm": one(), "head": mat(cfg["vocab"], C)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, layer["mixer"]
+        for k in ("1", "2"):
+            W.update({p + "norm" + k: one(), p + "norm" + k + "b": one(), p + "ls" + k: vec(C, 0.5), p + "rg" + k: mat(C, C),
+                      p + "rg" + k + ".b": vec(C, 0.5, 0.5)})
+        H, D, E = m["heads"], m["dim"], m["vdim"]
+        if layer["type"] == "latent_attention":
+            R, P = m["kv_rank"], m["rot_dim"]
+            W.update({p + "mix.q": mat(H * (D + P), C), p + "mix.dkv": mat(R + P, C), p + "mix.dkv.norm": vec(R),
+                      p + "mix.uk": mat(H * D, R), p + "mix.uv": mat(H * E, R), p + "mix.g": mat(H, C),
+                      p + "mix.o": mat(C, H * E)})
+        else:
+            G = m["kv_heads"]
+            W.update({p + "mix.q": mat(H * D, C), p + "mix.k": mat(G * D, C), p + "mix.v": mat(G * E, C),
+                      p + "mix.g": mat(H * E, C), p + "mix.o": mat(C, H * E)})
+            if layer["type"] == "attention_2":
+                W.update({p + "mix.q.b": vec(H * D, 0.0), p + "mix.k.b": vec(G * D, 0.0), p + "mix.v.b": vec(G * E, 0.0),
+                          p + "mix.q.norm": vec(H * D), p + "mix.k.norm": vec(G * D)})
+        F = layer["mlp"]["ff"]
+        W.update({p + "mlp.up": mat(F, C), p + "mlp.down": mat(C, F)})
+    return W
+
+
+def kelutar_attention_config(width, layers, heads, kv, dim, window, ff, vocab, max_positions):
+    """A Kelutar model whose every layer is its window attention with a dense feed-forward."""
+    cfg = kelutar_config(width, layers, heads, dim, window, ff, vocab, max_positions)
+    cfg["layers"] = [{"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                                                     "mask": {"size": window}, "scale": 1.0 / math.sqrt(dim)},
+                      "mlp": {"kind": "dense", "ff": ff}} for _ in range(layers)]
+    return cfg
+
+
+def bench_size_tokatar(name, width, layers, heads, kv, dim, block, ff, rank, rot, vocab, peaks, steps, warmup,
+                       prefill_batch=4, prompt=2048, decode_batches=(1, 8, 32), context=1024):
+    """Tokatar beside Kelutar with attention in every layer (the closest existing decoder: the same attention kernels,
+    squared-ReLU feed-forward, step function, cache and linears) at equal width, layer count, heads and feed-forward."""
+    from llark_b200.models.kelutar import KelutarConfig, KelutarForCausalLM
+    from llark_b200.models.tokatar import TokatarConfig, TokatarForCausalLM
+
+    flush = _Flush()
+    out = {"size": name, "width": width, "layers": layers, "heads": heads, "kv_heads": kv, "head_dim": dim, "block": block,
+           "ff": ff, "kv_rank": rank, "rot_dim": rot, "vocab": vocab,
+           "prefill": {"batch": prefill_batch, "prompt": prompt}, "decode": {"context": context}}
+    g = torch.Generator().manual_seed(0)
+    cfg = tokatar_config(width, layers, heads, kv, dim, block, ff, rank, rot, vocab)
+    tm = TokatarForCausalLM(TokatarConfig.from_dict(cfg), tokatar_random_weights(cfg, "cuda"), dtype=BF16)
+    tm.engine.max_positions = max(prompt, context) + 64
+    bench_native("tokatar", tm.engine, TOKATAR_OPS, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt,
+                 decode_batches, context)
+    del tm
+    torch.cuda.empty_cache()
+    kcfg = kelutar_attention_config(width, layers, heads, kv, dim, block, ff, vocab, max(prompt, context) + 64)
+    km = KelutarForCausalLM(KelutarConfig.from_dict(kcfg), kelutar_random_weights(kcfg, "cuda"), dtype=BF16)
+    bench_native("kelutar", km.engine, KELUTAR_OPS, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt,
+                 decode_batches, context)
+    del km
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_tokatar(args, peaks, peaks_kind, emit):
+    from llark_b200 import ops
+
+    ops.init()
+    t0 = time.time()
+    sizes = [s for s in TOKATAR_SIZES if not os.environ.get("LLARK_BENCH_SIZE") or s[0] == os.environ["LLARK_BENCH_SIZE"]]
+    results = [bench_size_tokatar(*s, peaks=peaks, steps=args.steps, warmup=max(args.warmup, 3)) for s in sizes]
+    head = results[0]
+    emit({"metric": "generation tokens/s, Tokatar beside an all-attention Kelutar at equal size (prefill of %d x %d tokens)"
+                    % (head["prefill"]["batch"], head["prefill"]["prompt"]),
+          "value": head["prefill"]["tokatar_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 3), "ms_per_step": head["prefill"]["tokatar_ms"], "higher_is_better": True,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
+          "config": {"model": "Tokatar " + head["size"], "l2": "256 MB fill between timed steps",
                      "peaks": peaks_kind, "hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]},
           "sizes": results, "wall_s": round(time.time() - t0, 1)})
 

@@ -214,6 +214,151 @@ __global__ void qkv_rotary_kernel(const float* __restrict__ src, long long ld, i
     }
 }
 
+template <typename T> __device__ __forceinline__ void st_quad(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void st_quad<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void st_quad<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 u;
+    u.x = pack_bf16x2(v[0], v[1]);
+    u.y = pack_bf16x2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// One head of n entries of which the first r are rotated, four entries at a time (16-byte loads, 16- / 8-byte stores).
+// Work item j of the head: interleaved pairs -> entries 4j .. 4j+3 (two pairs when inside the rotated zone); halves ->
+// entries 4j .. 4j+3 of the first half together with their partners r/2 + 4j .., then the entries behind the zone.
+// s: source row of the head; scale r_; w: norm weights of the head or NULL; cs: cos | sin per pair; o / o2: destinations.
+template <typename T>
+__device__ __forceinline__ void rotate_quads(const float* __restrict__ s, float r_, const float* __restrict__ w,
+                                             const float* __restrict__ cs, int r, int interleaved, int j,
+                                             T* __restrict__ o, T* __restrict__ o2) {
+    auto load = [&](int c, float (&v)[4]) {
+        const float4 a = *reinterpret_cast<const float4*>(s + c);
+        v[0] = a.x * r_, v[1] = a.y * r_, v[2] = a.z * r_, v[3] = a.w * r_;
+        if (w) {
+            const float4 b = *reinterpret_cast<const float4*>(w + c);
+            v[0] *= b.x, v[1] *= b.y, v[2] *= b.z, v[3] *= b.w;
+        }
+    };
+    auto store = [&](int c, const float (&v)[4]) {
+        st_quad(o + c, v);
+        if (o2) st_quad(o2 + c, v);
+    };
+    float a[4], b[4];
+    if (interleaved) {
+        const int c = 4 * j;
+        load(c, a);
+        if (c < r) {
+            const int p0 = c >> 1;
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const float co = cs[2 * (p0 + k)], si = cs[2 * (p0 + k) + 1];
+                const float u = a[2 * k], v = a[2 * k + 1];
+                a[2 * k] = u * co - v * si;
+                a[2 * k + 1] = v * co + u * si;
+            }
+        }
+        store(c, a);
+        return;
+    }
+    const int hq = r >> 1, nq = hq >> 2;  // quads in the first half of the zone
+    if (j < nq) {
+        load(4 * j, a);
+        load(hq + 4 * j, b);
+        float ua[4], vb[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float co = cs[2 * (4 * j + k)], si = cs[2 * (4 * j + k) + 1];
+            ua[k] = a[k] * co - b[k] * si;
+            vb[k] = b[k] * co + a[k] * si;
+        }
+        store(4 * j, ua);
+        store(hq + 4 * j, vb);
+    } else {
+        const int c = r + 4 * (j - nq);
+        load(c, a);
+        store(c, a);
+    }
+}
+
+// The same as qkv_rotary_kernel for sizes and addresses that allow four entries per access (checked by the launcher).
+template <typename T>
+__global__ void qkv_rotary4_kernel(const float* __restrict__ src, long long ld, int q_off, int k_off, int v_off,
+                                   const float* __restrict__ wq, const float* __restrict__ wk,
+                                   const float* __restrict__ qk_freq, int n_rot, int qk_interleaved,
+                                   const float* __restrict__ v_freq, int v_interleaved, T* __restrict__ qn,
+                                   T* __restrict__ kn, T* __restrict__ vv, T* __restrict__ kring, T* __restrict__ vring,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                   const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D, int E,
+                                   int cap, float eps) {
+    extern __shared__ float cs[];
+    __shared__ float red[2][32];
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const long long p = pos0[b] + (t - cu[b]);
+    const int hq = n_rot >> 1, hv = v_freq ? (E >> 1) : 0;
+    float* csv = cs + 2 * hq;
+    for (int i = threadIdx.x; i < hq; i += blockDim.x) sincosf((float)p * qk_freq[i], &cs[2 * i + 1], &cs[2 * i]);
+    for (int i = threadIdx.x; i < hv; i += blockDim.x) sincosf((float)p * v_freq[i], &csv[2 * i + 1], &csv[2 * i]);
+    const float* row = src + (long long)t * ld;
+    float rq = 1.f, rk = 1.f;
+    if (wq) {
+        float sq = 0.f, sk = 0.f;
+        for (int c = threadIdx.x; c < (H * D) >> 2; c += blockDim.x) {
+            const float4 a = reinterpret_cast<const float4*>(row + q_off)[c];
+            sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+        for (int c = threadIdx.x; c < (G * D) >> 2; c += blockDim.x) {
+            const float4 a = reinterpret_cast<const float4*>(row + k_off)[c];
+            sk += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+        if (l == 0) {
+            red[0][w] = sq;
+            red[1][w] = sk;
+        }
+        __syncthreads();
+        sq = sk = 0.f;
+        for (int i = 0; i < nw; ++i) {
+            sq += red[0][i];
+            sk += red[1][i];
+        }
+        rq = 1.0f / sqrtf(sq / (float)(H * D) + eps);
+        rk = 1.0f / sqrtf(sk / (float)(G * D) + eps);
+    } else {
+        __syncthreads();
+    }
+    T *rk_row = nullptr, *rv_row = nullptr;
+    if (kring) {
+        const long long e = (long long)slot[b] * cap + (p % cap);
+        rk_row = kring + e * G * D;
+        rv_row = vring + e * G * E;
+    }
+    const int iq = qk_interleaved ? D >> 2 : (hq >> 2) + ((D - n_rot) >> 2);  // work items of a q / k head
+    const int rv = v_freq ? E : 0;
+    const int iv = (v_interleaved || !v_freq) ? E >> 2 : (E >> 3);             // of a value head (halves: all of E rotates)
+    const int n_qk = (H + G) * iq;
+    for (int i = threadIdx.x; i < n_qk + G * iv; i += blockDim.x) {
+        if (i < n_qk) {
+            const int hh = i / iq, j = i - hh * iq;
+            const bool is_q = hh < H;
+            const int c0 = (is_q ? hh : hh - H) * D;
+            const float* w = is_q ? wq : wk;
+            rotate_quads<T>(row + (is_q ? q_off : k_off) + c0, is_q ? rq : rk, w ? w + c0 : nullptr, cs, n_rot,
+                            qk_interleaved, j, is_q ? qn + (long long)t * H * D + c0 : kn + (long long)t * G * D + c0,
+                            (!is_q && rk_row) ? rk_row + c0 : (T*)nullptr);
+        } else {
+            const int head = (i - n_qk) / iv, j = (i - n_qk) - head * iv;
+            const int c0 = head * E;
+            rotate_quads<T>(row + v_off + c0, 1.f, nullptr, csv, rv, v_interleaved, j, vv + (long long)t * G * E + c0,
+                            rv_row ? rv_row + c0 : (T*)nullptr);
+        }
+    }
+}
+
 // N consecutive elements -> float, with one 4 / 8 / 16-byte load per piece when `vec` (the address is then aligned to
 // the piece); scalar loads otherwise.
 template <typename T, int N>
@@ -660,17 +805,30 @@ extern "C" int llark_seq_qkv_rotary(const float* src, long long ld, int q_off, i
     if (kring && (!vring || cap <= 0)) return LLARK_EINVAL;
     const size_t smem = sizeof(float) * (size_t)(n_rot + (v_freq ? 2 * (E / 2) : 0));
     if (smem > 48 * 1024) return LLARK_EINVAL;
-    const int threads = 128;
-    if (act_fp32)
-        qkv_rotary_kernel<float><<<n_tok, threads, smem, st>>>(src, ld, q_off, k_off, v_off, wq, wk, qk_freq, n_rot,
-                                                               qk_interleaved, v_freq, v_interleaved, (float*)qn, (float*)kn,
-                                                               (float*)vv, (float*)kring, (float*)vring, tok_seq, cu, pos0,
-                                                               slot, H, G, D, E, cap, eps);
-    else
-        qkv_rotary_kernel<bf16_t><<<n_tok, threads, smem, st>>>(src, ld, q_off, k_off, v_off, wq, wk, qk_freq, n_rot,
-                                                                qk_interleaved, v_freq, v_interleaved, (bf16_t*)qn,
-                                                                (bf16_t*)kn, (bf16_t*)vv, (bf16_t*)kring, (bf16_t*)vring,
-                                                                tok_seq, cu, pos0, slot, H, G, D, E, cap, eps);
+    // Four entries per access when every head, zone and offset is a multiple of four entries (of eight for zones in halves)
+    // and the rows start on 16-byte boundaries.
+    const bool quads = D % 4 == 0 && E % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 && ld % 4 == 0 &&
+                       n_rot % (qk_interleaved ? 4 : 8) == 0 && (!v_freq || E % (v_interleaved ? 4 : 8) == 0) &&
+                       (((uintptr_t)src | (uintptr_t)qn | (uintptr_t)kn | (uintptr_t)vv | (uintptr_t)kring | (uintptr_t)vring |
+                         (uintptr_t)wq | (uintptr_t)wk) & 15) == 0;
+    // work items of a token: few tokens (decoding): as many threads as items, so that no thread walks a chain of dependent
+    // loads; many tokens: 256 threads, the grid fills the GPU anyway.
+    int items = (H + G) * (D - n_rot / 2) + G * (v_freq ? E - E / 2 : E);
+    if (quads) items /= 4;
+    int threads = n_tok >= 1024 ? 256 : (items + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+#define LLARK_ROTARY(KERNEL, T)                                                                                      \
+    KERNEL<T><<<n_tok, threads, smem, st>>>(src, ld, q_off, k_off, v_off, wq, wk, qk_freq, n_rot, qk_interleaved, v_freq, \
+                                            v_interleaved, (T*)qn, (T*)kn, (T*)vv, (T*)kring, (T*)vring, tok_seq, cu, pos0, \
+                                            slot, H, G, D, E, cap, eps)
+    if (quads) {
+        if (act_fp32) LLARK_ROTARY(qkv_rotary4_kernel, float);
+        else LLARK_ROTARY(qkv_rotary4_kernel, bf16_t);
+    } else {
+        if (act_fp32) LLARK_ROTARY(qkv_rotary_kernel, float);
+        else LLARK_ROTARY(qkv_rotary_kernel, bf16_t);
+    }
+#undef LLARK_ROTARY
     return check_launch();
 }
 

@@ -280,10 +280,81 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ x, const float* __r
 // x_out = x + rmsnorm(y * sigmoid(gate)) * w, and optionally the NEXT sublayer's input norm in the same pass:
 // x_act = rmsnorm(x_out) * w_next -> T. gate (optional) is a column slice [rows, gate_ld] of a fused projection. The gated
 // row stays in shared memory between its reduction and its use, and is replaced there by the new stream for the second
-// norm. VEC: C % 4 == 0 and every row 16-byte aligned.
+// norm.
 __device__ __forceinline__ float sigmoid_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-template <typename T, bool VEC>
+template <typename T> __device__ __forceinline__ void st4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void st4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    uint2 v;
+    v.x = pack_bf16x2(a, b);
+    v.y = pack_bf16x2(c, d);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
+// C % 4 == 0, rows 16-byte aligned, C <= 4 * NV * blockDim.x: the row lives in registers (NV float4 per thread) from the
+// first read to the last write; 16-byte loads, 16- / 8-byte stores.
+template <typename T, int NV>
+__global__ void gated_norm_add4_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                                       const float* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
+                                       const float* __restrict__ w_next, float* __restrict__ x_out, T* __restrict__ x_act,
+                                       int C, float eps) {
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    const int nv = C >> 2;
+    const float4* yr = reinterpret_cast<const float4*>(y + row * C);
+    const float4* gr = gate ? reinterpret_cast<const float4*>(gate + row * gate_ld) : nullptr;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * C);
+    float4 keep[NV], xv[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nv) {
+            float4 a = yr[v];
+            xv[i] = xr[v];
+            if (gr) {
+                const float4 g = gr[v];
+                a.x *= sigmoid_(g.x), a.y *= sigmoid_(g.y), a.z *= sigmoid_(g.z), a.w *= sigmoid_(g.w);
+            }
+            keep[i] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)C + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nv) {
+            const float4 a = keep[i], wv = reinterpret_cast<const float4*>(w)[v];
+            float4 o;
+            o.x = xv[i].x + a.x * r * wv.x, o.y = xv[i].y + a.y * r * wv.y;
+            o.z = xv[i].z + a.z * r * wv.z, o.w = xv[i].w + a.w * r * wv.w;
+            reinterpret_cast<float4*>(x_out + row * C)[v] = o;
+            keep[i] = o;
+            s2 += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+        }
+    }
+    if (!x_act) return;
+    s2 = block_sum(s2, red);
+    const float r2 = 1.0f / sqrtf(s2 / (float)C + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nv) {
+            const float4 o = keep[i], wn = reinterpret_cast<const float4*>(w_next)[v];
+            st4(x_act + row * C + 4 * v, o.x * r2 * wn.x, o.y * r2 * wn.y, o.z * r2 * wn.z, o.w * r2 * wn.w);
+        }
+    }
+}
+
+// Any C: the gated row stays in shared memory between its reduction and its use, and is replaced there by the new stream
+// for the second norm.
+template <typename T>
 __global__ void gated_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ y,
                                       const float* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
                                       const float* __restrict__ w_next, float* __restrict__ x_out, T* __restrict__ x_act,
@@ -296,46 +367,20 @@ __global__ void gated_norm_add_kernel(const float* __restrict__ x, const float* 
     const float* xr = x + row * C;
     float* xo = x_out + row * C;
     float ss = 0.f;
-    if constexpr (VEC) {
-        const int nv = C >> 2;
-        for (int v = threadIdx.x; v < nv; v += blockDim.x) {
-            float4 a = reinterpret_cast<const float4*>(yr)[v];
-            if (gr) {
-                const float4 g = reinterpret_cast<const float4*>(gr)[v];
-                a.x *= sigmoid_(g.x), a.y *= sigmoid_(g.y), a.z *= sigmoid_(g.z), a.w *= sigmoid_(g.w);
-            }
-            reinterpret_cast<float4*>(rowbuf)[v] = a;
-            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-        }
-    } else {
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
-            float a = yr[c];
-            if (gr) a *= sigmoid_(gr[c]);
-            rowbuf[c] = a;
-            ss = fmaf(a, a, ss);
-        }
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float a = yr[c];
+        if (gr) a *= sigmoid_(gr[c]);
+        rowbuf[c] = a;
+        ss = fmaf(a, a, ss);
     }
     ss = block_sum(ss, red);
     const float r = 1.0f / sqrtf(ss / (float)C + eps);
     float s2 = 0.f;
-    if constexpr (VEC) {
-        const int nv = C >> 2;
-        for (int v = threadIdx.x; v < nv; v += blockDim.x) {
-            const float4 a = reinterpret_cast<float4*>(rowbuf)[v];
-            const float4 xv = reinterpret_cast<const float4*>(xr)[v], wv = reinterpret_cast<const float4*>(w)[v];
-            float4 o;
-            o.x = xv.x + a.x * r * wv.x, o.y = xv.y + a.y * r * wv.y, o.z = xv.z + a.z * r * wv.z, o.w = xv.w + a.w * r * wv.w;
-            reinterpret_cast<float4*>(xo)[v] = o;
-            reinterpret_cast<float4*>(rowbuf)[v] = o;
-            s2 += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
-        }
-    } else {
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
-            const float o = xr[c] + rowbuf[c] * r * w[c];
-            xo[c] = o;
-            rowbuf[c] = o;
-            s2 = fmaf(o, o, s2);
-        }
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float o = xr[c] + rowbuf[c] * r * w[c];
+        xo[c] = o;
+        rowbuf[c] = o;
+        s2 = fmaf(o, o, s2);
     }
     if (!x_act) return;
     s2 = block_sum(s2, red);
@@ -836,32 +881,45 @@ extern "C" int llark_seq_gated_norm_add(const float* x, const float* y, const fl
                                         const float* w, const float* w_next, float* x_out, void* x_act, long long rows,
                                         int C, float eps, int act_fp32, cudaStream_t st) {
     if (rows <= 0 || C <= 0 || !x || !y || !w || !x_out || (x_act && !w_next)) return LLARK_EINVAL;
+    const bool vec = (C % 4 == 0) && C <= 4 * 4 * 512 && (!gate || gate_ld % 4 == 0) && ((uintptr_t)x % 16 == 0) &&
+                     ((uintptr_t)y % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)x_out % 16 == 0) &&
+                     (!gate || (uintptr_t)gate % 16 == 0) && (!x_act || ((uintptr_t)x_act % 16 == 0 && (uintptr_t)w_next % 16 == 0));
+    if (vec) {
+        const int nv = C / 4;
+        const int per = nv <= 256 ? 1 : (nv <= 1024 ? 2 : 4);  // float4 per thread: 256 .. 512 threads on wide rows
+        int threads = ((nv + per - 1) / per + 31) / 32 * 32;
+#define LLARK_GNA4(T, NV) \
+    gated_norm_add4_kernel<T, NV><<<(unsigned)rows, threads, 0, st>>>(x, y, gate, gate_ld, w, w_next, x_out, (T*)x_act, C, eps)
+        if (act_fp32) {
+            if (per == 1) LLARK_GNA4(float, 1);
+            else if (per == 2) LLARK_GNA4(float, 2);
+            else LLARK_GNA4(float, 4);
+        } else {
+            if (per == 1) LLARK_GNA4(bf16_t, 1);
+            else if (per == 2) LLARK_GNA4(bf16_t, 2);
+            else LLARK_GNA4(bf16_t, 4);
+        }
+#undef LLARK_GNA4
+        return check_launch();
+    }
     const size_t smem = sizeof(float) * (size_t)C;
     if (smem > 200 * 1024) return LLARK_EINVAL;
-    const bool vec = (C % 4 == 0) && (!gate || gate_ld % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) &&
-                     ((uintptr_t)w % 16 == 0) && ((uintptr_t)x_out % 16 == 0) && (!gate || (uintptr_t)gate % 16 == 0);
-    int threads = vec ? C / 4 : C;
-    threads = threads < 64 ? 64 : (threads > 512 ? 512 : (threads + 31) / 32 * 32);
-#define LLARK_GNA(T, V)                                                                                               \
+    int threads = C < 64 ? 64 : (C > 512 ? 512 : (C + 31) / 32 * 32);
+#define LLARK_GNA(T)                                                                                                 \
     do {                                                                                                              \
         if (smem > 48 * 1024) {                                                                                       \
-            cudaError_t e = cudaFuncSetAttribute(gated_norm_add_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+            cudaError_t e = cudaFuncSetAttribute(gated_norm_add_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                                  (int)smem);                                                          \
             if (e != cudaSuccess) {                                                                                   \
                 g_last_cuda_error = (int)e;                                                                           \
                 return LLARK_ECUDA;                                                                                   \
             }                                                                                                         \
         }                                                                                                             \
-        gated_norm_add_kernel<T, V><<<(unsigned)rows, threads, smem, st>>>(x, y, gate, gate_ld, w, w_next, x_out,     \
-                                                                           (T*)x_act, C, eps);                       \
+        gated_norm_add_kernel<T><<<(unsigned)rows, threads, smem, st>>>(x, y, gate, gate_ld, w, w_next, x_out,        \
+                                                                        (T*)x_act, C, eps);                          \
     } while (0)
-    if (act_fp32) {
-        if (vec) LLARK_GNA(float, true);
-        else LLARK_GNA(float, false);
-    } else {
-        if (vec) LLARK_GNA(bf16_t, true);
-        else LLARK_GNA(bf16_t, false);
-    }
+    if (act_fp32) LLARK_GNA(float);
+    else LLARK_GNA(bf16_t);
 #undef LLARK_GNA
     return check_launch();
 }

@@ -94,7 +94,8 @@ class TokatarEngine(LayerListEngine):
     def _run_layers(self, cache, x, st, residuals):
         eps = self.cfg.eps
         entries = cache.layers
-        h = ops.seq_rmsnorm_rows(x, None, entries[0]["pk"]["norm1"], eps, self.act)  # every later norm rides on a residual kernel
+        # the first input norm (one part over the width); every later one rides on a residual kernel
+        h = ops.seq_group_rmsnorm(x, entries[0]["pk"]["norm1"], 1, eps, out_dtype=self.act)
         for i, entry in enumerate(entries):
             pk = entry["pk"]
             nxt = entries[i + 1]["pk"]["norm1"] if i + 1 < len(entries) else None
@@ -116,5 +117,5 @@ class TokatarEngine(LayerListEngine):
         return ops.seq_gated_norm_add(x, y, w_post, self.cfg.eps, gate=gate, w_next=w_next, act=self.act)
 
     def _logits(self, x, rows):
-        hn = ops.seq_rmsnorm_rows(x, rows, self.final_norm, self.cfg.eps, self.act)
+        hn = ops.seq_group_rmsnorm(x, self.final_norm, 1, self.cfg.eps, out_dtype=self.act, rows=rows)
         return ops.linear(hn, self.head, out_dtype=F32)[:, :self.cfg.vocab]

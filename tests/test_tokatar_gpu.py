@@ -165,7 +165,7 @@ PORTIONS = ([150], [1] * 150, [100] + [1] * 50, [31, 2, 2, 65, 1, 1, 30, 18])
 
 
 # ------------------------------------------------------------------------------------------------ mechanisms alone
-@pytest.mark.parametrize("C", [51, 72, 1024])
+@pytest.mark.parametrize("C", [51, 72, 1024, 2048, 4100, 8196])
 def test_gate_norm_scale_and_sum_with_the_next_input_norm(C):
     from llark_b200 import ops
 
@@ -195,35 +195,37 @@ def test_gate_norm_scale_and_sum_with_the_next_input_norm(C):
 
 @pytest.mark.parametrize("H,G,D,E,n_rot,interleaved,norm,vrot", [
     (4, 2, 16, 12, 8, False, False, False), (3, 3, 10, 6, 10, True, True, True), (2, 1, 6, 8, 0, False, True, False),
-    (3, 1, 32, 32, 32, True, False, True), (5, 5, 7, 4, 6, False, True, True)])
+    (3, 1, 32, 32, 32, True, False, True), (5, 5, 7, 4, 6, False, True, True), (2, 2, 24, 16, 16, False, True, True),
+    (3, 1, 12, 8, 4, True, True, True), (2, 1, 64, 64, 64, False, False, False)])
 def test_projection_norm_and_rotation_of_queries_keys_and_values(H, G, D, E, n_rot, interleaved, norm, vrot):
     from llark_b200 import ops
 
     g = torch.Generator().manual_seed(H * D + E)
     T, pos0 = 9, 37
     n = H * D + G * D + G * E
-    src = torch.randn(T, n + 3, generator=g, dtype=F64)
     wq, wk = 1.0 + 0.3 * torch.randn(H * D, generator=g, dtype=F64), 1.0 + 0.3 * torch.randn(G * D, generator=g, dtype=F64)
     f = to.frequencies(n_rot, 50.0) if n_rot else torch.zeros(0, dtype=F64)
     fv = to.frequencies(E, 50.0)
     layout = "interleaved" if interleaved else "halves"
     pos = torch.arange(pos0, pos0 + T)
-    q, k, v = src[:, 3:3 + H * D], src[:, 3 + H * D:3 + (H + G) * D], src[:, 3 + (H + G) * D:]
-    if norm:
-        q, k = to.rms(q, 1e-5) * wq, to.rms(k, 1e-5) * wk
-    q, k = to.turn(q.reshape(T, H, D), pos, f, layout), to.turn(k.reshape(T, G, D), pos, f, layout)
-    v = v.reshape(T, G, E)
-    if vrot:
-        v = to.turn(v, pos, fv, layout)
     d = _dev()
     st = _layout([T], [pos0], [0])
-    for act in (F32, BF16):
-        gq, gk, gv = ops.seq_qkv_rotary(src.to(d, F32), 3, 3 + H * D, 3 + (H + G) * D, H, G, D, E, 1e-5, act, st,
-                                        wq=wq.to(d, F32) if norm else None, wk=wk.to(d, F32) if norm else None,
-                                        qk_freq=f.to(d, F32) if n_rot else None, qk_interleaved=interleaved,
-                                        v_freq=fv.to(d, F32) if vrot else None, v_interleaved=interleaved)
-        tol = 2e-6 if act == F32 else 4e-3
-        assert _rel(gq, q.reshape(T, -1)) < tol and _rel(gk, k.reshape(T, -1)) < tol and _rel(gv, v.reshape(T, -1)) < tol
+    for off in (3, 4):  # columns in front of q: an odd offset takes the scalar kernel, a multiple of four the 16-byte one
+        src = torch.randn(T, n + off + (-(n + off)) % 4, generator=g, dtype=F64)
+        q, k, v = src[:, off:off + H * D], src[:, off + H * D:off + (H + G) * D], src[:, off + (H + G) * D:off + n]
+        if norm:
+            q, k = to.rms(q, 1e-5) * wq, to.rms(k, 1e-5) * wk
+        q, k = to.turn(q.reshape(T, H, D), pos, f, layout), to.turn(k.reshape(T, G, D), pos, f, layout)
+        v = v.reshape(T, G, E)
+        if vrot:
+            v = to.turn(v, pos, fv, layout)
+        for act in (F32, BF16):
+            gq, gk, gv = ops.seq_qkv_rotary(src.to(d, F32), off, off + H * D, off + (H + G) * D, H, G, D, E, 1e-5, act, st,
+                                            wq=wq.to(d, F32) if norm else None, wk=wk.to(d, F32) if norm else None,
+                                            qk_freq=f.to(d, F32) if n_rot else None, qk_interleaved=interleaved,
+                                            v_freq=fv.to(d, F32) if vrot else None, v_interleaved=interleaved)
+            tol = 2e-6 if act == F32 else 4e-3
+            assert _rel(gq, q.reshape(T, -1)) < tol and _rel(gk, k.reshape(T, -1)) < tol and _rel(gv, v.reshape(T, -1)) < tol
 
 
 LAYERS_ALONE = {
