@@ -542,14 +542,14 @@ def tokatar_config(width, layers, heads, kv, dim, block, ff, rank, rot, vocab):
     scale = 1.0 / math.sqrt(dim)
     att = {"type": "attention", "mlp": mlp,
            "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": block}, "scale": scale,
-                     "softcap": 50.0, "rot": {"base": 250000.0, "dims": dim,
-                                              "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
+                     "softcap": 30.0, "rot": {"base": 100000.0, "dims": dim,
+                                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
     att2 = {"type": "attention_2", "mlp": mlp,
             "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "mask": {"size": block}, "scale": scale,
-                      "rot": {"base": 500000.0, "dims": dim}}}
+                      "rot": {"base": 1000000.0, "dims": dim}}}
     lat = {"type": "latent_attention", "mlp": mlp,
            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank,
-                     "scale": 1.0 / math.sqrt(dim + rot), "rot": {"base": 20000.0, "dims": rot}}}
+                     "scale": 1.0 / math.sqrt(dim + rot), "rot": {"base": 10000.0, "dims": rot}}}
     return {"architecture": "Tokatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "embedding": {"scale": math.sqrt(width)}, "layers": [(att, att2, lat, att)[i % 4] for i in range(layers)]}
 

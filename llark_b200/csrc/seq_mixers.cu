@@ -426,6 +426,7 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
     for (int d = threadIdx.x; d < D; d += blockDim.x) sq[d] = ldf(qn + ((long long)t * H + h) * D + d);
     __syncthreads();
     const long long ring_base = (long long)slot[b] * cap;
+    const int row_b = cu[b];
     const int ring0 = (int)(lo % cap);  // ring entry of the window's first key; key jj sits at ring0 + jj (- cap), as
                                         // the keys of a window never outnumber the ring's entries
     const long long first_here = from_ring_only ? p + 1 : p0;  // positions >= first_here are rows of this step
@@ -442,11 +443,25 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
         if (jj < nkeys) {
             int ridx = ring0 + jj;
             if (ridx >= cap) ridx -= cap;
-            const T* kr = j >= first_here ? kn + ((long long)(cu[b] + (j - p0)) * G + g) * D
+            const T* kr = j >= first_here ? kn + ((long long)(row_b + (j - p0)) * G + g) * D
                                           : kring + ((ring_base + ridx) * G + g) * D;
             float dot = 0.f;
             if (kvec) {
-                for (int d = 0; d < D; d += KV) {
+                // eight 16-byte pieces of the key row in flight at a time: every lane reads a row of its own, so a piece
+                // is a trip to L2 and the loop is bound by how many of them overlap. The raw pieces wait in registers.
+                int d = 0;
+                for (; d + 8 * KV <= D; d += 8 * KV) {
+                    uint4 raw[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(kr + d + u * KV);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+                        for (int x = 0; x < KV; ++x) dot = fmaf(sq[d + u * KV + x], ldf(e + x), dot);
+                    }
+                }
+                for (; d < D; d += KV) {
                     float kk[KV];
                     load_run<T, KV>(kr + d, kk, true);
 #pragma unroll
@@ -469,12 +484,31 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
         sp[warp * 32 + lane] = pj;
         __syncwarp();
         const int cnt = nkeys - tile * 32 < 32 ? nkeys - tile * 32 : 32;
-        for (int k = 0; k < cnt; ++k) {
+        auto value_row = [&](int k) -> const T* {
             const long long j2 = lo + tile * 32 + k;
             int ridx = ring0 + tile * 32 + k;
             if (ridx >= cap) ridx -= cap;
-            const T* vr = j2 >= first_here ? vv + ((long long)(cu[b] + (j2 - p0)) * G + g) * E
-                                           : vring + ((ring_base + ridx) * G + g) * E;
+            return j2 >= first_here ? vv + ((long long)(row_b + (j2 - p0)) * G + g) * E
+                                    : vring + ((ring_base + ridx) * G + g) * E;
+        };
+        int k = 0;
+        if (vvec) {
+            // the rows of eight keys are requested before the first is used: one trip to L2 per batch, not per key
+            constexpr int VB = DPL <= 4 ? 8 : 4;
+            for (; k + VB <= cnt; k += VB) {
+                float vx[VB][DPL];
+#pragma unroll
+                for (int u = 0; u < VB; ++u) load_run<T, DPL>(value_row(k + u) + lane * DPL, vx[u], true);
+#pragma unroll
+                for (int u = 0; u < VB; ++u) {
+                    const float pk = sp[warp * 32 + k + u];
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pk, vx[u][i], acc[i]);
+                }
+            }
+        }
+        for (; k < cnt; ++k) {
+            const T* vr = value_row(k);
             const float pk = sp[warp * 32 + k];
             if (vvec) {
                 float vx[DPL];

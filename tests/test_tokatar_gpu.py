@@ -237,7 +237,7 @@ LAYERS_ALONE = {
                     _att2(3, 1, 6, 10, 1, _rot(20.0, 4, (2.0, 1.0, 2.0, 16))), _att2(2, 1, 32, 32, 48, _rot(1e4, 32)),
                     _att2(2, 2, 64, 64, 70, _rot(1e3, 64))],
     "latent_attention": [_lat(3, 6, 4, 5, 12, 30.0), _lat(2, 16, 8, 16, 24, 100.0), _lat(3, 5, 2, 7, 9, 7.0),
-                         _lat(4, 32, 16, 24, 48, 2e4)],
+                         _lat(4, 32, 16, 24, 48, 3e4)],
 }
 
 

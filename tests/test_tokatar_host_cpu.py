@@ -62,7 +62,7 @@ def test_registry_and_tables():
 
 
 @pytest.mark.parametrize("dims,base,scaling", [
-    (8, 100.0, None), (48, 1e4, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}),
+    (8, 100.0, None), (40, 1e4, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}),
     (16, 30.0, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 40}), (6, 5e5, {"factor": 2.0, "low": 2.0, "high": 3.0, "original": 10})])
 def test_frequency_table(dims, base, scaling):
     from llark_b200.mixers import rotary_frequencies
