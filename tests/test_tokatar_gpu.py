@@ -559,6 +559,72 @@ def test_long_prompt_and_long_decoding():
         assert _logit_err(torch.cat(out), want[idx + list(range(380, 520))]) < _tol(dtype)
 
 
+def _random_config(seed):
+    """A configuration drawn at random: 2 to 5 layers of any kind in any order, widths and head sizes on and off the
+    16-byte and tensor-core routes, key heads that divide the heads, blocks from 1 position to more than the sequence or no
+    mask at all, rotation over the whole head or a part, with or without rescaled frequencies and soft cap."""
+    import random
+
+    r = random.Random(seed)
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        kind = r.choice(["attention", "attention_2", "latent_attention"])
+        ff = r.choice([40, 64, 100]) if r.random() < 0.8 else None
+        if kind == "latent_attention":
+            layers.append(_lat(r.choice([1, 2, 3, 4, 8]), r.choice([6, 8, 16, 32]), r.choice([2, 4, 8, 16]), r.choice([8, 12, 24, 32]),
+                               r.choice([12, 24, 48, 56]), r.choice([100.0, 3e4, 1e6]), mlp=ff))
+            continue
+        H = r.choice([1, 2, 4, 6, 8])
+        G = r.choice([g for g in (1, 2, 3, 4, 6, 8) if H % g == 0])
+        D = r.choice([8, 12, 16, 32, 64, 80])
+        E = r.choice([D, D, 16, 24, 64])
+        scaling = (r.choice([2.0, 4.0, 8.0]), 1.0, r.choice([2.0, 4.0]), r.choice([16, 64, 4096])) if r.random() < 0.5 else None
+        rot = _rot(r.choice([100.0, 1e4, 3e5]), r.choice([D, D, D // 4 * 2, 4]), scaling)
+        size = r.choice([None, 1, 3, 16, 50, 64, 65, 128, 1000])
+        softcap = r.choice([5.0, 30.0]) if kind == "attention" and r.random() < 0.7 else None
+        layers.append(_att(H, G, D, E, size, rot, softcap=softcap, scale=r.choice([None, 0.1, 0.3]), mlp=ff, kind=kind))
+    return _cfg(layers, vocab=r.choice([37, 100, 256]), width=r.choice([48, 51, 64, 100, 136]), eps=r.choice([1e-5, 1e-6]),
+                scale=r.choice([1.0, 8.0]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed):
+    """Each request alone in one step, as a prompt with its last tokens decoded, and three unequal requests together."""
+    cfg = _random_config(seed)
+    W = to.random_weights(cfg, seed=seed)
+    reqs = [_tokens(n, cfg["vocab"], seed + n) for n in (5, 70, 150)]
+    want = [to.forward(cfg, W, q) for q in reqs]
+    for dtype in (F32, BF16):
+        m = _model(cfg, W, dtype)
+        if seed % 2:
+            m.engine.max_positions = 200  # rings no longer than the request may grow
+        cache = m.new_cache(n_slots=2)
+        tol = 1e-4 if dtype == F32 else 0.1
+        for q, w in zip(reqs, want):
+            s = cache.alloc()
+            assert _logit_err(m.engine.step(cache, [s], [q], want=[list(range(len(q)))]), w) < tol
+            cache.release(s)
+            cut = max(1, len(q) - 30)
+            s = cache.alloc()
+            out = [m.engine.step(cache, [s], [q[:cut]], want=[list(range(cut))])]
+            out += [m.engine.step(cache, [s], [[t]]) for t in q[cut:]]
+            cache.release(s)
+            assert _logit_err(torch.cat(out), w) < tol
+        slots = [cache.alloc() for _ in reqs]
+        cuts = [max(1, len(q) - 4) for q in reqs]
+        lg = m.engine.step(cache, slots, [q[:c] for q, c in zip(reqs, cuts)], want=[list(range(c)) for c in cuts])
+        outs, at = [], 0
+        for c in cuts:
+            outs.append([lg[at:at + c]])
+            at += c
+        for k in range(4):
+            lg = m.engine.step(cache, slots, [[q[c + k]] for q, c in zip(reqs, cuts)])
+            for i in range(3):
+                outs[i].append(lg[i:i + 1])
+        for i in range(3):
+            assert _logit_err(torch.cat(outs[i]), want[i]) < tol
+
+
 def test_checkpoint_folder_registry_and_greedy_generation(tmp_path):
     """config.json + model.safetensors -> the registry picks the class; generate() and the scheduler reproduce the
     restatement's greedy continuation (fp32, so that the argmax is the restatement's)."""
